@@ -1,0 +1,415 @@
+#!/usr/bin/env python
+"""Benchmark of the int8 quantized-linear hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+
+Workload (config.workload): the decode sweep on LLaMA-2-7B-shaped projections at M=1 -
+QLinear K->N in {4096->4096, 4096->11008, 11008->4096}, weights ~ N(0, 0.02) quantized per
+output channel to int8, f32 activations ~ N(0, 1).  One step = one M=1 forward of every layer
+of a rotation set (several independently drawn copies of each shape, > L2 in total) so the
+weights come from HBM, not L2.  metric = int8-weight streaming rate in GB/s, counting the
+algorithmic bytes N*K + 4N + 4K + 4N per forward.  The same line carries the M=2048 prefill
+figure (TOPS) under "prefill".
+
+N > 1 (torchrun, one rank per GPU): every rank holds its own column shard of N-times-wider layers
+(weak scaling: per-GPU weight bytes fixed), computes its output slice and the slices are
+all-gathered over NCCL.
+
+--impl reference times the CPU restatement of the reference's Rayon/AVX2 path (oracle/) on the
+host cores: at M=1 the reference's row split gives exactly one task, hence one thread.
+"""
+import argparse
+import ctypes as C
+import importlib
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008)]  # (N, K)
+REPLICAS = 4  # copies of each shape in the rotation set: 4 * 107 MB = 428 MB > 126 MB L2
+PREFILL_SHAPES = [(11008, 4096), (4096, 11008)]
+PREFILL_M = 2048
+
+
+def algorithmic_bytes(n, k, m, bias=False):
+    return n * k + 4 * n + (4 * n if bias else 0) + 4 * m * k + 4 * m * n
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100", "-i", str(self.gpu_index)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [t.strip() for t in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm: the CPU restatement of the reference's path, on the host cores
+# ---------------------------------------------------------------------------------------------
+def cpu_forward_rate(seconds_budget, reps_cap=1000):
+    """Times M=1 forwards of one layer of each shape with the oracle (AVX2 path, one thread: the
+    reference parallelises over input rows only, src/nn/quantized.rs:179-182).  Returns
+    (GB/s, cores, sample text, seconds of CPU work)."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    rng = np.random.default_rng(2)
+    layers = []
+    for (n, k) in SHAPES:
+        q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        s = (np.abs(rng.standard_normal(n)) * 1e-3 + 1e-4).astype(np.float32)
+        x = rng.standard_normal((1, k)).astype(np.float32)
+        layers.append((q, s, x))
+    for (q, s, x) in layers:  # warm-up, also pages the arrays in
+        oracle.forward(q, s, None, x, threads=1, use_avx2=-1)
+    total_bytes, total_t, reps = 0, 0.0, 0
+    while total_t < seconds_budget and reps < reps_cap:
+        for (q, s, x) in layers:
+            t0 = time.perf_counter()
+            oracle.forward(q, s, None, x, threads=1, use_avx2=-1)
+            total_t += time.perf_counter() - t0
+            total_bytes += algorithmic_bytes(q.shape[0], q.shape[1], 1)
+        reps += 1
+    avx = bool(oracle.lib().nne_ref_has_avx2_fma())
+    sample = (f"{reps} passes of one M=1 forward per shape {SHAPES} "
+              f"({'AVX2/FMA' if avx else 'portable'} dot, 1 thread = all the reference's row "
+              f"split allows at M=1; host has {os.cpu_count()} cores)")
+    return total_bytes / total_t / 1e9, 1, sample, total_t
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    rng = np.random.default_rng(2)
+    layers = []
+    for (n, k) in SHAPES:
+        q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+        s = (np.abs(rng.standard_normal(n)) * 1e-3 + 1e-4).astype(np.float32)
+        x = rng.standard_normal((1, k)).astype(np.float32)
+        layers.append((q, s, x))
+    step_bytes = sum(algorithmic_bytes(n, k, 1) for (n, k) in SHAPES)
+
+    def step():
+        for (q, s, x) in layers:
+            oracle.forward(q, s, None, x, threads=1, use_avx2=-1)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = step_bytes * args.steps / dt / 1e9
+    sample = ("each step = one M=1 forward of one layer per shape (bounded sample of the rotation "
+              "set: 1 of 4 copies); C restatement of the reference's Rayon/AVX2 path, 1 thread "
+              f"(the row split gives one task at M=1); host has {os.cpu_count()} cores")
+    print(json.dumps({
+        "impl": "reference", "metric": "qlinear_int8_weight_stream_rate_m1", "value": value,
+        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config2-decode-7B-projections-M1", "shapes_NK": SHAPES, "m": 1},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": 1, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+# ---------------------------------------------------------------------------------------------
+# native arm
+# ---------------------------------------------------------------------------------------------
+def run_native(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run, one rank per GPU")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    nne = importlib.import_module("neural-network-engine_b200")
+    lib = nne.load()
+    ctx = nne.CudaContext(local_rank)
+    peaks = measured_peaks()
+
+    def make_layer(n, k, seed):
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed)
+        w = torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * 0.02
+        h = C.c_void_p()
+        st = lib.nne_qlinear_create_from_f32_dev(ctx.handle, w.data_ptr(), None, n, k,
+                                                 torch.cuda.current_stream().cuda_stream, C.byref(h))
+        if st != 0:
+            raise RuntimeError(f"layer create failed: {nne._lib.last_error()}")
+        torch.cuda.synchronize()
+        del w
+        return h
+
+    # rotation set: REPLICAS independently drawn copies of each shape (this rank's shard when N>1)
+    layers = []
+    for rep in range(REPLICAS):
+        for si, (n, k) in enumerate(SHAPES):
+            h = make_layer(n, k, 2 + 1000 * rank + 10 * rep + si)
+            g = torch.Generator(device=dev)
+            g.manual_seed(100 + 10 * rep + si)  # activations are replicated: same on every rank
+            x = torch.randn(1, k, generator=g, device=dev, dtype=torch.float32)
+            y_full = torch.zeros(world, n, device=dev, dtype=torch.float32)  # gathered slices
+            layers.append({"h": h, "n": n, "k": k, "x": x, "y": y_full, "y_own": y_full[rank]})
+    step_bytes = sum(algorithmic_bytes(L["n"], L["k"], 1) for L in layers)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        s = stream.cuda_stream
+        for L in layers:
+            st = lib.nne_qlinear_forward_dev(L["h"], L["x"].data_ptr(), 1, L["k"],
+                                             L["y_own"].data_ptr(), s)
+            if st != 0:
+                raise RuntimeError(nne._lib.last_error())
+            if world > 1:
+                dist.all_gather_into_tensor(L["y"].view(-1), L["y_own"])
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+
+    # device-timed region: K steps back to back on one stream
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    launches0 = lib.nne_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    launches = lib.nne_launch_count() - launches0
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop() if rank == 0 else None
+    value = step_bytes * world * args.steps / (ms * 1e-3) / 1e9
+    per_launch_us = ms * 1e3 / (args.steps * len(layers))
+    achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9  # one GPU's kernels
+
+    # end-to-end: the host-pointer entry point (what QLinear::forward calls), pinned host buffers,
+    # H2D of x and D2H of y inside every call.
+    host = []
+    for L in layers:
+        xh = torch.empty(1, L["k"], dtype=torch.float32).pin_memory()
+        xh.copy_(L["x"].cpu())
+        yh = torch.empty(1, L["n"], dtype=torch.float32).pin_memory()
+        host.append((xh, yh))
+
+    def e2e_step():
+        for L, (xh, yh) in zip(layers, host):
+            st = lib.nne_qlinear_forward_host(L["h"], xh.data_ptr(), 1, L["k"], yh.data_ptr())
+            if st != 0:
+                raise RuntimeError(nne._lib.last_error())
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e2e_steps = max(args.steps, 5)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = step_bytes * world * e2e_steps / e2e_s / 1e9
+    h2d = sum(4 * L["k"] for L in layers)
+    d2h = sum(4 * L["n"] for L in layers)
+
+    # prefill (M = 2048) on the tensor-core kernel, when it is built in
+    prefill = None
+    if world == 1:
+        prefill = run_prefill(nne, lib, ctx, dev, make_layer, peaks, args)
+
+    out = None
+    if rank == 0:
+        cpu_v, cpu_cores, cpu_sample, _ = cpu_forward_rate(seconds_budget=8.0)
+        out = {
+            "metric": "qlinear_int8_weight_stream_rate_m1", "value": value, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "config2-decode-7B-projections-M1", "shapes_NK": SHAPES,
+                       "m": 1, "replicas_per_shape": REPLICAS, "layers_per_step": len(layers),
+                       "weight_bytes_per_step_per_gpu": sum(L["n"] * L["k"] for L in layers),
+                       "l2": "rotation set of distinct weights larger than the 126 MB L2",
+                       "parallelism": "1 GPU" if world == 1 else
+                       f"column shards over {world} GPUs + NCCL all-gather of output slices"},
+            "roofline": {"bound": "hbm", "kernel": "qgemv_kernel", "achieved": achieved,
+                         "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                         "frac_of_nominal_8000": achieved / 8000.0,
+                         "avg_launch_us": per_launch_us, "traffic": None},
+            "cpu_baseline": {"value": cpu_v, "unit": "GB/s", "cores": cpu_cores, "kind": "port",
+                             "sample": cpu_sample},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "api": "nne_qlinear_forward_host (pinned host x and y, per call H2D + D2H)"},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if prefill is not None:
+            out["prefill"] = prefill
+        print(json.dumps(out))
+    for L in layers:
+        lib.nne_qlinear_destroy(L["h"])
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):
+    """M = 2048 forward of the two FFN shapes; TFLOP/s = 2*M*N*K / device time."""
+    import torch
+    res = {"m": PREFILL_M, "shapes_NK": PREFILL_SHAPES, "cases": []}
+    stream = torch.cuda.current_stream()
+    tot_flops, tot_ms = 0.0, 0.0
+    for si, (n, k) in enumerate(PREFILL_SHAPES):
+        h = make_layer(n, k, 3 + si)
+        kind = lib.nne_qlinear_kernel_for(h, PREFILL_M)
+        if kind != 2:
+            lib.nne_qlinear_destroy(h)
+            return {"unavailable": "tensor-core kernel not built for this shape", "kernel": kind}
+        x = torch.randn(PREFILL_M, k, device=dev, dtype=torch.float32)
+        y = torch.empty(PREFILL_M, n, device=dev, dtype=torch.float32)
+
+        def fwd():
+            st = lib.nne_qlinear_forward_dev(h, x.data_ptr(), PREFILL_M, k, y.data_ptr(),
+                                             stream.cuda_stream)
+            if st != 0:
+                raise RuntimeError(nne._lib.last_error())
+
+        for _ in range(3):
+            fwd()
+        torch.cuda.synchronize()
+        iters = 20
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            fwd()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        flops = 2.0 * PREFILL_M * n * k
+        res["cases"].append({"n": n, "k": k, "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12})
+        tot_flops += flops
+        tot_ms += ms
+        lib.nne_qlinear_destroy(h)
+        del x, y
+    tf = tot_flops / (tot_ms * 1e-3) / 1e12
+    res["roofline"] = {"bound": "tensor", "kernel": "qlinear_prefill_kernel", "achieved": tf,
+                       "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                       "frac": tf / peaks["bf16_tflops"], "peak_source": peaks["source"],
+                       "frac_of_nominal_2250": tf / 2250.0}
+    res["value"] = tf
+    res["unit"] = "TFLOP/s"
+    res["dtype"] = "bf16 x bf16 -> f32 (int8 weights dequantized to bf16 in shared memory)"
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,152 @@
+/*
+ * nne_cuda.h - C ABI of the B200 (sm_100a) backend for the int8 quantized-linear path of
+ * elvin-mark/neural-network-engine.
+ *
+ * This is the whole boundary a host language binds: plain pointers and sizes, no C++ or torch
+ * types.  The reference has no FFI for this path today; every entry point below names the
+ * reference item (path within the reference project : line) whose work it takes over, which
+ * is what the Rust side `src/gpu/cuda/ffi.rs` declares in an `extern "C"` block.
+ *
+ * Conventions
+ *  - Every function returns an nne_status (0 = OK).  No C++ exception crosses the boundary.
+ *  - `*_host` buffers are ordinary host memory owned by the caller; the call returns after the
+ *    result is in place.  `*_dev` buffers are device pointers on the context's device; the call
+ *    is asynchronous on `stream` (a cudaStream_t passed as void*, NULL = the legacy default
+ *    stream) and never synchronises.
+ *  - Weights are [N, K] row-major (N = out_features, K = in_features, K contiguous), exactly
+ *    the layout of `QLinear.qweight` (src/nn/quantized.rs:80-81).
+ *  - A layer handle is immutable after creation, so concurrent forwards on one handle are
+ *    safe as long as each call uses its own stream and its own x/y buffers.  `_host` forwards
+ *    serialise on a per-context mutex.
+ *  - There is no CPU fallback: without a usable sm_100 device every call fails with
+ *    NNE_ERR_CUDA or NNE_ERR_UNSUPPORTED.
+ */
+#ifndef NNE_CUDA_H_
+#define NNE_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define NNE_API __attribute__((visibility("default")))
+#else
+#define NNE_API
+#endif
+
+/* Status codes.  The Rust side maps 1 -> EngineError::InvalidArgument (src/error.rs:41-42),
+ * 2 -> EngineError::ShapeMismatch (src/error.rs:11-15), everything else ->
+ * EngineError::GpuError(String) (src/error.rs:47-48) carrying nne_last_error's text. */
+typedef enum nne_status {
+    NNE_OK = 0,
+    NNE_ERR_INVALID_ARGUMENT = 1,
+    NNE_ERR_SHAPE_MISMATCH = 2,
+    NNE_ERR_CUDA = 3,
+    NNE_ERR_NCCL = 4,
+    NNE_ERR_TIMEOUT = 5,
+    NNE_ERR_OUT_OF_MEMORY = 6,
+    NNE_ERR_UNSUPPORTED = 7
+} nne_status;
+
+typedef struct nne_ctx nne_ctx;         /* one per device: streams, staging, SM count   */
+typedef struct nne_qlinear nne_qlinear; /* one device-resident int8 layer               */
+typedef struct nne_shard nne_shard;     /* one rank's column slice of a sharded layer   */
+
+/* ---- status text -------------------------------------------------------------------------- */
+
+/* Static description of a status code. */
+NNE_API const char *nne_status_string(int status);
+/* Copies the calling thread's last error message (NUL-terminated, truncated to n) into buf.
+ * Takes the place of the String inside EngineError::GpuError (src/error.rs:47-48). */
+NNE_API int nne_last_error(char *buf, size_t n);
+
+/* ---- context ------------------------------------------------------------------------------
+ * Plays the role of Arc<GpuContext> of the existing device backend (src/gpu/context.rs:20-59,
+ * src/gpu/layers.rs:12-16): created once, shared by every layer placed on that device.       */
+NNE_API int nne_cuda_ctx_create(int device, nne_ctx **out);
+NNE_API int nne_cuda_ctx_destroy(nne_ctx *ctx);
+/* Device facts the host side sizes its work with.  Any out pointer may be NULL. */
+NNE_API int nne_cuda_ctx_info(const nne_ctx *ctx, int *device, int *sm_count, int *cc_major,
+                              int *cc_minor, size_t *total_mem_bytes);
+
+/* ---- quantize / dequantize ----------------------------------------------------------------
+ * nne_quantize_rows replaces the row loop of QLinear::from_linear (src/nn/quantized.rs:107-127):
+ * per row absmax, scale = max>0 ? max/127 : 1, inv = 1/scale, q = round_half_away(v*inv)
+ * clamped to [-128,127], NaN -> 0.  Codes and scales are bit-identical to the reference.      */
+NNE_API int nne_quantize_rows(nne_ctx *ctx, const float *w_host, size_t rows, size_t cols,
+                              int8_t *q_host, float *scales_host);
+NNE_API int nne_quantize_rows_dev(nne_ctx *ctx, const float *w_dev, size_t rows, size_t cols,
+                                  int8_t *q_dev, float *scales_dev, void *stream);
+
+/* nne_quantize_tensor replaces Int8Tensor::from_raw (src/nn/quantized.rs:32-57): ONE scale for
+ * all n elements.  The _dev form needs a 4-byte device scratch word for the grid-wide absmax;
+ * it is part of the context.  *scale_dev receives the f32 scale.                              */
+NNE_API int nne_quantize_tensor(nne_ctx *ctx, const float *v_host, size_t n, int8_t *q_host,
+                                float *scale_out);
+NNE_API int nne_quantize_tensor_dev(nne_ctx *ctx, const float *v_dev, size_t n, int8_t *q_dev,
+                                    float *scale_dev, void *stream);
+
+/* nne_dequantize_rows replaces Int8Tensor::dequantize (src/nn/quantized.rs:60-67; rows = 1,
+ * cols = n, one scale) and the weight loop of QLinear::to_linear (src/nn/quantized.rs:200-209;
+ * one scale per row): out = (f32)q * scale[row].                                              */
+NNE_API int nne_dequantize_rows(nne_ctx *ctx, const int8_t *q_host, const float *scales_host,
+                                size_t rows, size_t cols, float *out_host);
+NNE_API int nne_dequantize_rows_dev(nne_ctx *ctx, const int8_t *q_dev, const float *scales_dev,
+                                    size_t rows, size_t cols, float *out_dev, void *stream);
+
+/* ---- layer --------------------------------------------------------------------------------
+ * nne_qlinear_create_from_f32 replaces QLinear::from_linear (src/nn/quantized.rs:92-141):
+ * uploads the f32 weight [N,K] (and bias [N] or NULL), quantizes ON DEVICE and keeps codes,
+ * scales and bias resident.  The _dev form takes device pointers (the f32 weight is not kept).
+ * nne_qlinear_create_from_i8 builds the same handle from the public fields of an existing
+ * QLinear (src/nn/quantized.rs:79-88), e.g. after Clone or a load from disk.                   */
+NNE_API int nne_qlinear_create_from_f32(nne_ctx *ctx, const float *w_host,
+                                        const float *bias_host_or_null, size_t n, size_t k,
+                                        nne_qlinear **out);
+NNE_API int nne_qlinear_create_from_f32_dev(nne_ctx *ctx, const float *w_dev,
+                                            const float *bias_dev_or_null, size_t n, size_t k,
+                                            void *stream, nne_qlinear **out);
+NNE_API int nne_qlinear_create_from_i8(nne_ctx *ctx, const int8_t *q_host,
+                                       const float *scales_host, const float *bias_host_or_null,
+                                       size_t n, size_t k, nne_qlinear **out);
+NNE_API int nne_qlinear_destroy(nne_qlinear *ql);
+
+/* Fills the host copies the reference keeps as pub fields `qweight` and `scales`
+ * (src/nn/quantized.rs:80-83; read by tests/nn/quantization_tests.rs:38-39).  Either pointer
+ * may be NULL. */
+NNE_API int nne_qlinear_download(const nne_qlinear *ql, int8_t *q_host, float *scales_host);
+/* in_features / out_features / has_bias and the device pointers of the resident tensors. */
+NNE_API int nne_qlinear_info(const nne_qlinear *ql, size_t *n, size_t *k, int *has_bias,
+                             const int8_t **q_dev, const float **scales_dev,
+                             const float **bias_dev);
+/* QLinear::memory_bytes (src/nn/quantized.rs:230-237): N*K + 4N (+4N with bias). */
+NNE_API size_t nne_qlinear_memory_bytes(const nne_qlinear *ql);
+
+/* nne_qlinear_forward_host replaces the compute of QLinear::forward_quantized
+ * (src/nn/quantized.rs:164-193) for an input already flattened to [m, k]:
+ * y[r,j] = (sum_i x[r,i] * q[j,i]) * scales[j] (+ bias[j]).  `k` is the caller's last input
+ * dimension and is checked against in_features as the reference does (:156-162), returning
+ * NNE_ERR_SHAPE_MISMATCH.  m = 0 is valid and does nothing.  Copies x up, runs, copies y back. */
+NNE_API int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, size_t k,
+                                     float *y_host);
+/* Same contraction on device-resident x [m,k] and y [m,n], asynchronous on `stream`. */
+NNE_API int nne_qlinear_forward_dev(nne_qlinear *ql, const float *x_dev, size_t m, size_t k,
+                                    float *y_dev, void *stream);
+/* Same, but writes y with a row stride of `ldy` floats (ldy >= n): used by a column shard to
+ * write its slice straight into the gathered [m, N_total] layout. */
+NNE_API int nne_qlinear_forward_dev_strided(nne_qlinear *ql, const float *x_dev, size_t m,
+                                            size_t k, float *y_dev, size_t ldy, void *stream);
+
+/* Which kernel a forward of m rows on this layer dispatches to: 1 = streaming GEMV (small m),
+ * 2 = tcgen05/TMEM tensor-core kernel, 3 = generic kernel for shapes the others do not take. */
+NNE_API int nne_qlinear_kernel_for(const nne_qlinear *ql, size_t m);
+/* Number of kernels this library has launched in the calling process (all contexts). */
+NNE_API uint64_t nne_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNE_CUDA_H_ */

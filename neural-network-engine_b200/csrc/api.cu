@@ -1,0 +1,537 @@
+// extern "C" entry points of the nne_cuda library (declared in include/nne_cuda.h): argument
+// checks, device memory ownership, host<->device staging and kernel dispatch.  The arithmetic
+// lives in quantize.cu, gemv.cu and prefill.cu.
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+
+namespace nne {
+
+std::atomic<uint64_t> g_launches{0};
+
+std::string &last_error_ref() {
+    thread_local std::string s;
+    return s;
+}
+
+int fail(int status, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    last_error_ref() = buf;
+    return status;
+}
+
+int GrowBuf::reserve(size_t bytes) {
+    if (bytes <= cap) return NNE_OK;
+    if (ptr) {
+        cudaFree(ptr);
+        ptr = nullptr;
+        cap = 0;
+    }
+    size_t want = bytes + bytes / 4;  // headroom so a slowly growing m does not reallocate
+    want = (want + 255) & ~(size_t)255;
+    NNE_CUDA_TRY(cudaMalloc(&ptr, want));
+    cap = want;
+    return NNE_OK;
+}
+
+void GrowBuf::release() {
+    if (ptr) cudaFree(ptr);
+    ptr = nullptr;
+    cap = 0;
+}
+
+namespace {
+
+bool mul_overflows(size_t a, size_t b, size_t *out) { return __builtin_mul_overflow(a, b, out); }
+
+bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int check_layer(const nne_qlinear *ql) {
+    if (!ql || !ql->ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null layer handle");
+    return NNE_OK;
+}
+
+int alloc_layer(nne_ctx *ctx, size_t n, size_t k, bool has_bias, nne_qlinear **out) {
+    size_t nk;
+    if (mul_overflows(n, k, &nk)) return fail(NNE_ERR_INVALID_ARGUMENT, "n*k overflows size_t");
+    nne_qlinear *ql = new (std::nothrow) nne_qlinear();
+    if (!ql) return fail(NNE_ERR_OUT_OF_MEMORY, "host allocation failed");
+    ql->ctx = ctx;
+    ql->device = ctx->device;
+    ql->n = n;
+    ql->k = k;
+    cudaError_t e = cudaMalloc(&ql->q, nk ? nk : 1);
+    if (e == cudaSuccess) e = cudaMalloc(&ql->scales, (n ? n : 1) * sizeof(float));
+    if (e == cudaSuccess && has_bias) e = cudaMalloc(&ql->bias, (n ? n : 1) * sizeof(float));
+    if (e != cudaSuccess) {
+        int st = fail(e == cudaErrorMemoryAllocation ? NNE_ERR_OUT_OF_MEMORY : NNE_ERR_CUDA,
+                      "device allocation for a %zu x %zu layer failed: %s", n, k,
+                      cudaGetErrorString(e));
+        cudaGetLastError();
+        nne_qlinear_destroy(ql);
+        return st;
+    }
+    *out = ql;
+    return NNE_OK;
+}
+
+// Kernel choice for a forward of m rows.  1 = streaming GEMV, 2 = tensor-core, 3 = generic.
+int pick_kernel(const nne_qlinear *ql, size_t m, const float *x, const float *y) {
+    const bool base_ok = aligned(ql->q, 16) && (x == nullptr || aligned(x, 16)) &&
+                         (y == nullptr || aligned(y, 4));
+    if (m > 16 && base_ok && prefill_supports(ql, m)) return 2;
+    if (base_ok && gemv_supports(ql->n, ql->k, m)) return 1;
+    return 3;
+}
+
+int forward_dev(nne_qlinear *ql, const float *x, size_t m, size_t k, float *y, size_t ldy,
+                cudaStream_t s) {
+    NNE_TRY(check_layer(ql));
+    if (k != ql->k)
+        return fail(NNE_ERR_SHAPE_MISMATCH, "shape mismatch: expected [%zu], got [%zu]", ql->k, k);
+    if (ldy < ql->n) return fail(NNE_ERR_INVALID_ARGUMENT, "ldy %zu < out_features %zu", ldy, ql->n);
+    size_t t;
+    if (mul_overflows(m, ql->k, &t) || mul_overflows(m, ldy, &t))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "m*k or m*ldy overflows size_t");
+    if (m == 0 || ql->n == 0) return NNE_OK;
+    if (!x || !y) return fail(NNE_ERR_INVALID_ARGUMENT, "null activation or output pointer");
+    NNE_TRY(use_ctx(ql->ctx));
+    if (ql->k == 0) {
+        // Empty contraction: dot = 0, y = 0*scale (+bias), as the reference's loops produce.
+        return launch_generic(ql->ctx, ql->q, ql->scales, ql->bias, x, y, ql->n, 0, m, ldy, s);
+    }
+    switch (pick_kernel(ql, m, x, y)) {
+        case 2: return launch_prefill(ql, x, y, m, ldy, s);
+        case 1:
+            return launch_gemv(ql->ctx, ql->q, ql->scales, ql->bias, x, y, ql->n, ql->k, m, ldy, s);
+        default:
+            return launch_generic(ql->ctx, ql->q, ql->scales, ql->bias, x, y, ql->n, ql->k, m, ldy,
+                                  s);
+    }
+}
+
+}  // namespace
+}  // namespace nne
+
+using namespace nne;
+
+extern "C" {
+
+const char *nne_status_string(int status) {
+    switch (status) {
+        case NNE_OK: return "ok";
+        case NNE_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case NNE_ERR_SHAPE_MISMATCH: return "shape mismatch";
+        case NNE_ERR_CUDA: return "CUDA error";
+        case NNE_ERR_NCCL: return "NCCL error";
+        case NNE_ERR_TIMEOUT: return "timeout";
+        case NNE_ERR_OUT_OF_MEMORY: return "out of memory";
+        case NNE_ERR_UNSUPPORTED: return "unsupported";
+        default: return "unknown status";
+    }
+}
+
+int nne_last_error(char *buf, size_t n) {
+    if (!buf || n == 0) return NNE_ERR_INVALID_ARGUMENT;
+    const std::string &s = last_error_ref();
+    size_t c = s.size() < n - 1 ? s.size() : n - 1;
+    memcpy(buf, s.data(), c);
+    buf[c] = 0;
+    return NNE_OK;
+}
+
+uint64_t nne_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int nne_cuda_ctx_create(int device, nne_ctx **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(NNE_ERR_CUDA, "no usable CUDA device: %s", cudaGetErrorString(e));
+    }
+    if (device < 0 || device >= count)
+        return fail(NNE_ERR_INVALID_ARGUMENT, "device %d out of range (have %d)", device, count);
+    NNE_CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    NNE_CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(NNE_ERR_UNSUPPORTED,
+                    "device %d is sm_%d%d; this library holds sm_100a code only and has no fallback",
+                    device, prop.major, prop.minor);
+    nne_ctx *ctx = new nne_ctx();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->cc_major = prop.major;
+    ctx->cc_minor = prop.minor;
+    ctx->total_mem = prop.totalGlobalMem;
+    ctx->smem_optin = prop.sharedMemPerBlockOptin;
+    e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->absmax_word, 256);
+    if (e != cudaSuccess) {
+        int st = fail(NNE_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
+        nne_cuda_ctx_destroy(ctx);
+        return st;
+    }
+    *out = ctx;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_cuda_ctx_destroy(nne_ctx *ctx) {
+    NNE_GUARD_BEGIN
+    if (!ctx) return NNE_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaStreamDestroy(ctx->stream);
+    }
+    ctx->stage_a.release();
+    ctx->stage_b.release();
+    ctx->stage_c.release();
+    ctx->xbf16.release();
+    if (ctx->absmax_word) cudaFree(ctx->absmax_word);
+    delete ctx;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_cuda_ctx_info(const nne_ctx *ctx, int *device, int *sm_count, int *cc_major, int *cc_minor,
+                      size_t *total_mem_bytes) {
+    if (!ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null context");
+    if (device) *device = ctx->device;
+    if (sm_count) *sm_count = ctx->sm_count;
+    if (cc_major) *cc_major = ctx->cc_major;
+    if (cc_minor) *cc_minor = ctx->cc_minor;
+    if (total_mem_bytes) *total_mem_bytes = ctx->total_mem;
+    return NNE_OK;
+}
+
+// ---- quantize ---------------------------------------------------------------------------------
+
+int nne_quantize_rows_dev(nne_ctx *ctx, const float *w_dev, size_t rows, size_t cols, int8_t *q_dev,
+                          float *scales_dev, void *stream) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    size_t t;
+    if (mul_overflows(rows, cols, &t) || mul_overflows(t, sizeof(float), &t))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "rows*cols overflows size_t");
+    if (rows == 0) return NNE_OK;
+    if (!scales_dev || (cols && (!w_dev || !q_dev)))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null device pointer");
+    return launch_quantize_rows(ctx, w_dev, rows, cols, q_dev, scales_dev, (cudaStream_t)stream);
+    NNE_GUARD_END
+}
+
+int nne_quantize_rows(nne_ctx *ctx, const float *w_host, size_t rows, size_t cols, int8_t *q_host,
+                      float *scales_host) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    size_t nk, bytes;
+    if (mul_overflows(rows, cols, &nk) || mul_overflows(nk, sizeof(float), &bytes))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "rows*cols overflows size_t");
+    if (rows == 0) return NNE_OK;
+    if (!scales_host || (nk && (!w_host || !q_host)))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null host pointer");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    NNE_TRY(ctx->stage_a.reserve(bytes ? bytes : 4));
+    NNE_TRY(ctx->stage_b.reserve(nk ? nk : 4));
+    NNE_TRY(ctx->stage_c.reserve(rows * sizeof(float)));
+    cudaStream_t s = ctx->stream;
+    if (bytes) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, w_host, bytes, cudaMemcpyHostToDevice, s));
+    NNE_TRY(launch_quantize_rows(ctx, (const float *)ctx->stage_a.ptr, rows, cols,
+                                 (int8_t *)ctx->stage_b.ptr, (float *)ctx->stage_c.ptr, s));
+    if (nk) NNE_CUDA_TRY(cudaMemcpyAsync(q_host, ctx->stage_b.ptr, nk, cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaMemcpyAsync(scales_host, ctx->stage_c.ptr, rows * sizeof(float),
+                                 cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_quantize_tensor_dev(nne_ctx *ctx, const float *v_dev, size_t n, int8_t *q_dev,
+                            float *scale_dev, void *stream) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    if (!scale_dev || (n && (!v_dev || !q_dev)))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null device pointer");
+    return launch_quantize_tensor(ctx, v_dev, n, q_dev, scale_dev, ctx->absmax_word,
+                                  (cudaStream_t)stream);
+    NNE_GUARD_END
+}
+
+int nne_quantize_tensor(nne_ctx *ctx, const float *v_host, size_t n, int8_t *q_host,
+                        float *scale_out) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    size_t bytes;
+    if (mul_overflows(n, sizeof(float), &bytes))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "n overflows size_t");
+    if (!scale_out || (n && (!v_host || !q_host)))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null host pointer");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    NNE_TRY(ctx->stage_a.reserve(bytes ? bytes : 4));
+    NNE_TRY(ctx->stage_b.reserve(n ? n : 4));
+    NNE_TRY(ctx->stage_c.reserve(sizeof(float)));
+    cudaStream_t s = ctx->stream;
+    if (n) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, v_host, bytes, cudaMemcpyHostToDevice, s));
+    NNE_TRY(launch_quantize_tensor(ctx, (const float *)ctx->stage_a.ptr, n,
+                                   (int8_t *)ctx->stage_b.ptr, (float *)ctx->stage_c.ptr,
+                                   ctx->absmax_word, s));
+    if (n) NNE_CUDA_TRY(cudaMemcpyAsync(q_host, ctx->stage_b.ptr, n, cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaMemcpyAsync(scale_out, ctx->stage_c.ptr, sizeof(float), cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_dequantize_rows_dev(nne_ctx *ctx, const int8_t *q_dev, const float *scales_dev, size_t rows,
+                            size_t cols, float *out_dev, void *stream) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    size_t t;
+    if (mul_overflows(rows, cols, &t) || mul_overflows(t, sizeof(float), &t))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "rows*cols overflows size_t");
+    if (rows == 0 || cols == 0) return NNE_OK;
+    if (!q_dev || !scales_dev || !out_dev)
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null device pointer");
+    return launch_dequantize_rows(ctx, q_dev, scales_dev, rows, cols, out_dev, (cudaStream_t)stream);
+    NNE_GUARD_END
+}
+
+int nne_dequantize_rows(nne_ctx *ctx, const int8_t *q_host, const float *scales_host, size_t rows,
+                        size_t cols, float *out_host) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    size_t nk, bytes;
+    if (mul_overflows(rows, cols, &nk) || mul_overflows(nk, sizeof(float), &bytes))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "rows*cols overflows size_t");
+    if (nk == 0) return NNE_OK;
+    if (!q_host || !scales_host || !out_host)
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null host pointer");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    NNE_TRY(ctx->stage_a.reserve(bytes));
+    NNE_TRY(ctx->stage_b.reserve(nk));
+    NNE_TRY(ctx->stage_c.reserve(rows * sizeof(float)));
+    cudaStream_t s = ctx->stream;
+    NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_b.ptr, q_host, nk, cudaMemcpyHostToDevice, s));
+    NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_c.ptr, scales_host, rows * sizeof(float),
+                                 cudaMemcpyHostToDevice, s));
+    NNE_TRY(launch_dequantize_rows(ctx, (const int8_t *)ctx->stage_b.ptr,
+                                   (const float *)ctx->stage_c.ptr, rows, cols,
+                                   (float *)ctx->stage_a.ptr, s));
+    NNE_CUDA_TRY(cudaMemcpyAsync(out_host, ctx->stage_a.ptr, bytes, cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+// ---- layer ------------------------------------------------------------------------------------
+
+int nne_qlinear_create_from_f32_dev(nne_ctx *ctx, const float *w_dev, const float *bias_dev_or_null,
+                                    size_t n, size_t k, void *stream, nne_qlinear **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    NNE_TRY(use_ctx(ctx));
+    if (n && k && !w_dev) return fail(NNE_ERR_INVALID_ARGUMENT, "null weight pointer");
+    nne_qlinear *ql = nullptr;
+    NNE_TRY(alloc_layer(ctx, n, k, bias_dev_or_null != nullptr, &ql));
+    cudaStream_t s = (cudaStream_t)stream;
+    int st = launch_quantize_rows(ctx, w_dev, n, k, ql->q, ql->scales, s);
+    if (st == NNE_OK && bias_dev_or_null && n) {
+        cudaError_t e = cudaMemcpyAsync(ql->bias, bias_dev_or_null, n * sizeof(float),
+                                        cudaMemcpyDeviceToDevice, s);
+        if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "bias copy failed: %s", cudaGetErrorString(e));
+    }
+    if (st == NNE_OK) st = prefill_prepare_layer(ql);
+    if (st != NNE_OK) {
+        nne_qlinear_destroy(ql);
+        return st;
+    }
+    *out = ql;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_create_from_f32(nne_ctx *ctx, const float *w_host, const float *bias_host_or_null,
+                                size_t n, size_t k, nne_qlinear **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    NNE_TRY(use_ctx(ctx));
+    size_t nk, bytes;
+    if (mul_overflows(n, k, &nk) || mul_overflows(nk, sizeof(float), &bytes))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "n*k overflows size_t");
+    if (nk && !w_host) return fail(NNE_ERR_INVALID_ARGUMENT, "null weight pointer");
+    nne_qlinear *ql = nullptr;
+    NNE_TRY(alloc_layer(ctx, n, k, bias_host_or_null != nullptr, &ql));
+    int st = NNE_OK;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        cudaStream_t s = ctx->stream;
+        st = ctx->stage_a.reserve(bytes ? bytes : 4);
+        cudaError_t e = cudaSuccess;
+        if (st == NNE_OK && bytes)
+            e = cudaMemcpyAsync(ctx->stage_a.ptr, w_host, bytes, cudaMemcpyHostToDevice, s);
+        if (st == NNE_OK && e == cudaSuccess)
+            st = launch_quantize_rows(ctx, (const float *)ctx->stage_a.ptr, n, k, ql->q, ql->scales, s);
+        if (st == NNE_OK && e == cudaSuccess && bias_host_or_null && n)
+            e = cudaMemcpyAsync(ql->bias, bias_host_or_null, n * sizeof(float),
+                                cudaMemcpyHostToDevice, s);
+        if (st == NNE_OK && e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (st == NNE_OK && e != cudaSuccess)
+            st = fail(NNE_ERR_CUDA, "layer upload failed: %s", cudaGetErrorString(e));
+    }
+    if (st == NNE_OK) st = prefill_prepare_layer(ql);
+    if (st != NNE_OK) {
+        nne_qlinear_destroy(ql);
+        return st;
+    }
+    *out = ql;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_create_from_i8(nne_ctx *ctx, const int8_t *q_host, const float *scales_host,
+                               const float *bias_host_or_null, size_t n, size_t k,
+                               nne_qlinear **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    NNE_TRY(use_ctx(ctx));
+    size_t nk;
+    if (mul_overflows(n, k, &nk)) return fail(NNE_ERR_INVALID_ARGUMENT, "n*k overflows size_t");
+    if ((nk && !q_host) || (n && !scales_host))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null codes or scales pointer");
+    nne_qlinear *ql = nullptr;
+    NNE_TRY(alloc_layer(ctx, n, k, bias_host_or_null != nullptr, &ql));
+    cudaError_t e = cudaSuccess;
+    {
+        std::lock_guard<std::mutex> lock(ctx->mu);
+        cudaStream_t s = ctx->stream;
+        if (nk) e = cudaMemcpyAsync(ql->q, q_host, nk, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess && n)
+            e = cudaMemcpyAsync(ql->scales, scales_host, n * sizeof(float), cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess && n && bias_host_or_null)
+            e = cudaMemcpyAsync(ql->bias, bias_host_or_null, n * sizeof(float),
+                                cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    }
+    int st = NNE_OK;
+    if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "layer upload failed: %s", cudaGetErrorString(e));
+    if (st == NNE_OK) st = prefill_prepare_layer(ql);
+    if (st != NNE_OK) {
+        nne_qlinear_destroy(ql);
+        return st;
+    }
+    *out = ql;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_destroy(nne_qlinear *ql) {
+    NNE_GUARD_BEGIN
+    if (!ql) return NNE_OK;
+    cudaSetDevice(ql->device);
+    prefill_release_layer(ql);
+    if (ql->own) {
+        if (ql->q) cudaFree(ql->q);
+        if (ql->scales) cudaFree(ql->scales);
+        if (ql->bias) cudaFree(ql->bias);
+    }
+    delete ql;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_download(const nne_qlinear *ql, int8_t *q_host, float *scales_host) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(check_layer(ql));
+    NNE_TRY(use_ctx(ql->ctx));
+    std::lock_guard<std::mutex> lock(ql->ctx->mu);
+    cudaStream_t s = ql->ctx->stream;
+    if (q_host && ql->n && ql->k)
+        NNE_CUDA_TRY(cudaMemcpyAsync(q_host, ql->q, ql->n * ql->k, cudaMemcpyDeviceToHost, s));
+    if (scales_host && ql->n)
+        NNE_CUDA_TRY(cudaMemcpyAsync(scales_host, ql->scales, ql->n * sizeof(float),
+                                     cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_info(const nne_qlinear *ql, size_t *n, size_t *k, int *has_bias,
+                     const int8_t **q_dev, const float **scales_dev, const float **bias_dev) {
+    NNE_TRY(check_layer(ql));
+    if (n) *n = ql->n;
+    if (k) *k = ql->k;
+    if (has_bias) *has_bias = ql->bias != nullptr;
+    if (q_dev) *q_dev = ql->q;
+    if (scales_dev) *scales_dev = ql->scales;
+    if (bias_dev) *bias_dev = ql->bias;
+    return NNE_OK;
+}
+
+size_t nne_qlinear_memory_bytes(const nne_qlinear *ql) {
+    if (!ql) return 0;
+    return ql->n * ql->k + ql->n * sizeof(float) + (ql->bias ? ql->n * sizeof(float) : 0);
+}
+
+int nne_qlinear_kernel_for(const nne_qlinear *ql, size_t m) {
+    if (!ql || !ql->ctx) return 0;
+    return pick_kernel(ql, m, nullptr, nullptr);
+}
+
+int nne_qlinear_forward_dev(nne_qlinear *ql, const float *x_dev, size_t m, size_t k, float *y_dev,
+                            void *stream) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(check_layer(ql));
+    return forward_dev(ql, x_dev, m, k, y_dev, ql->n, (cudaStream_t)stream);
+    NNE_GUARD_END
+}
+
+int nne_qlinear_forward_dev_strided(nne_qlinear *ql, const float *x_dev, size_t m, size_t k,
+                                    float *y_dev, size_t ldy, void *stream) {
+    NNE_GUARD_BEGIN
+    return forward_dev(ql, x_dev, m, k, y_dev, ldy, (cudaStream_t)stream);
+    NNE_GUARD_END
+}
+
+int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, size_t k,
+                             float *y_host) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(check_layer(ql));
+    if (k != ql->k)
+        return fail(NNE_ERR_SHAPE_MISMATCH, "shape mismatch: expected [%zu], got [%zu]", ql->k, k);
+    size_t xb, yb;
+    if (mul_overflows(m, ql->k, &xb) || mul_overflows(xb, sizeof(float), &xb) ||
+        mul_overflows(m, ql->n, &yb) || mul_overflows(yb, sizeof(float), &yb))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "m*k or m*n overflows size_t");
+    if (m == 0 || ql->n == 0) return NNE_OK;
+    if ((xb && !x_host) || !y_host) return fail(NNE_ERR_INVALID_ARGUMENT, "null host pointer");
+    nne_ctx *ctx = ql->ctx;
+    NNE_TRY(use_ctx(ctx));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    NNE_TRY(ctx->stage_a.reserve(xb ? xb : 4));
+    NNE_TRY(ctx->stage_b.reserve(yb));
+    cudaStream_t s = ctx->stream;
+    if (xb) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, x_host, xb, cudaMemcpyHostToDevice, s));
+    NNE_TRY(forward_dev(ql, (const float *)ctx->stage_a.ptr, m, k, (float *)ctx->stage_b.ptr, ql->n, s));
+    NNE_CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_b.ptr, yb, cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+}  // extern "C"

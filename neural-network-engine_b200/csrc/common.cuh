@@ -1,0 +1,131 @@
+// Shared host-side plumbing of the nne_cuda library: status/error text, the per-device context,
+// the layer handle, and the launch counter.  Kernels live in quantize.cu, gemv.cu, prefill.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <mutex>
+#include <string>
+
+#include "../../include/nne_cuda.h"
+
+namespace nne {
+
+// ---- thread-local error text -------------------------------------------------------------
+std::string &last_error_ref();
+int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+
+#define NNE_CUDA_TRY(expr)                                                                   \
+    do {                                                                                     \
+        cudaError_t e__ = (expr);                                                            \
+        if (e__ != cudaSuccess) {                                                            \
+            int st__ = (e__ == cudaErrorMemoryAllocation) ? NNE_ERR_OUT_OF_MEMORY            \
+                                                          : NNE_ERR_CUDA;                    \
+            return ::nne::fail(st__, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e__), \
+                               __FILE__, __LINE__);                                          \
+        }                                                                                    \
+    } while (0)
+
+#define NNE_TRY(expr)                      \
+    do {                                   \
+        int st__ = (expr);                 \
+        if (st__ != NNE_OK) return st__;   \
+    } while (0)
+
+// Every extern "C" body is wrapped so that no C++ exception can cross the boundary.
+#define NNE_GUARD_BEGIN try {
+#define NNE_GUARD_END                                                              \
+    }                                                                              \
+    catch (const std::bad_alloc &) {                                               \
+        return ::nne::fail(NNE_ERR_OUT_OF_MEMORY, "host allocation failed");       \
+    }                                                                              \
+    catch (const std::exception &ex) {                                             \
+        return ::nne::fail(NNE_ERR_INVALID_ARGUMENT, "exception: %s", ex.what());  \
+    }                                                                              \
+    catch (...) {                                                                  \
+        return ::nne::fail(NNE_ERR_INVALID_ARGUMENT, "unknown exception");         \
+    }
+
+// ---- launch counter ----------------------------------------------------------------------
+extern std::atomic<uint64_t> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
+
+// Checks the launch that was just issued.
+#define NNE_LAUNCH_CHECK()                                                               \
+    do {                                                                                 \
+        ::nne::count_launch();                                                           \
+        cudaError_t e__ = cudaGetLastError();                                            \
+        if (e__ != cudaSuccess)                                                          \
+            return ::nne::fail(NNE_ERR_CUDA, "kernel launch failed: %s (%s:%d)",         \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);             \
+    } while (0)
+
+// A device buffer that only ever grows; used for host-call staging and kernel workspaces.
+struct GrowBuf {
+    void *ptr = nullptr;
+    size_t cap = 0;
+    int reserve(size_t bytes);
+    void release();
+};
+
+}  // namespace nne
+
+// ---- opaque handles ------------------------------------------------------------------------
+struct nne_ctx {
+    int device = 0;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    size_t total_mem = 0;
+    size_t smem_optin = 0;
+    cudaStream_t stream = nullptr;  // used by the *_host entry points
+    std::mutex mu;                  // serialises *_host calls and workspace growth
+    nne::GrowBuf stage_a, stage_b, stage_c;  // host-call staging (inputs / outputs)
+    unsigned int *absmax_word = nullptr;     // 4-byte scratch for the per-tensor absmax
+    nne::GrowBuf xbf16;                      // bf16 copy of the activations for the tensor path
+};
+
+struct nne_qlinear {
+    nne_ctx *ctx = nullptr;
+    int device = 0;           // copy of ctx->device, so destroy works after the context is gone
+    size_t n = 0, k = 0;
+    int8_t *q = nullptr;      // [n, k] row-major codes
+    float *scales = nullptr;  // [n]
+    float *bias = nullptr;    // [n] or null
+    bool own = true;
+    void *tmap_w = nullptr;   // host copy of the TMA descriptor of q (tensor path), or null
+};
+
+namespace nne {
+
+// Sets the calling thread's current device to the context's.
+inline int use_ctx(const nne_ctx *ctx) {
+    if (!ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null context");
+    NNE_CUDA_TRY(cudaSetDevice(ctx->device));
+    return NNE_OK;
+}
+
+// kernels' host launchers (defined next to the kernels) ---------------------------------------
+int launch_quantize_rows(nne_ctx *ctx, const float *w, size_t rows, size_t cols, int8_t *q,
+                         float *scales, cudaStream_t s);
+int launch_quantize_tensor(nne_ctx *ctx, const float *v, size_t n, int8_t *q, float *scale_dev,
+                           unsigned int *absmax_word, cudaStream_t s);
+int launch_dequantize_rows(nne_ctx *ctx, const int8_t *q, const float *scales, size_t rows,
+                           size_t cols, float *out, cudaStream_t s);
+
+bool gemv_supports(size_t n, size_t k, size_t m);
+int launch_gemv(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
+                const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
+                cudaStream_t s);
+int launch_generic(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
+                   const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
+                   cudaStream_t s);
+
+bool prefill_supports(const nne_qlinear *ql, size_t m);
+int prefill_prepare_layer(nne_qlinear *ql);  // builds the weight TMA descriptor
+void prefill_release_layer(nne_qlinear *ql);
+int launch_prefill(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
+                   cudaStream_t s);
+
+}  // namespace nne

@@ -1,0 +1,84 @@
+"""The reference's own tests for this path (tests/nn/quantization_tests.rs), replayed through
+the host mirror of nn::quantized on the GPU, with the same assertions and thresholds."""
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def new_linear(nne, seed, in_f, out_f):
+    """Linear::new(in, out): random weights and bias of the usual fan-in scale."""
+    bound = 1.0 / np.sqrt(in_f)
+    w = oracle.normal(seed, 0, (out_f, in_f), 0.0, bound / np.sqrt(3.0))
+    b = oracle.normal(seed, 1, (out_f,), 0.0, bound / np.sqrt(3.0))
+    return nne.Linear(w, b)
+
+
+def linear_forward_f32(lin, x):
+    """f32 Linear::forward (src/nn/linear.rs:47-55), the comparison target of the tests."""
+    y = x.reshape(-1, lin.in_features).astype(np.float32) @ lin.weight.T
+    if lin.bias is not None:
+        y = y + lin.bias
+    return y.reshape(list(x.shape[:-1]) + [lin.out_features]).astype(np.float32)
+
+
+def test_int8_tensor_roundtrip(nne, ctx):
+    raw = oracle.normal(21, 0, (32, 64))
+    q_tensor = nne.Int8Tensor.from_raw(raw, ctx)
+    assert q_tensor.shape == [32, 64]
+    assert len(q_tensor.data) == 32 * 64
+    assert q_tensor.scale > 0.0
+    dequant = q_tensor.dequantize(ctx)
+    assert dequant.shape == raw.shape
+    rmse = np.sqrt(np.mean((raw - dequant) ** 2, dtype=np.float32))
+    assert rmse < 0.05, f"INT8 quantization error too high: RMSE = {rmse}"
+
+
+def test_qlinear_from_linear_and_forward(nne, ctx):
+    linear = new_linear(nne, 22, 64, 128)
+    qlinear = nne.QLinear.from_linear(linear, ctx)
+    assert qlinear.in_features == 64 and qlinear.out_features == 128
+    assert len(qlinear.qweight) == 64 * 128 and len(qlinear.scales) == 128
+    x_2d = oracle.normal(22, 2, (8, 64))
+    out_fp32 = linear_forward_f32(linear, x_2d)
+    out_int8 = qlinear.forward(x_2d)
+    assert out_fp32.shape == out_int8.shape
+    cos = float((out_fp32 * out_int8).sum() / (np.linalg.norm(out_fp32) * np.linalg.norm(out_int8)))
+    assert cos > 0.995, f"QLinear 2D cosine similarity too low: {cos}"
+    x_3d = oracle.normal(22, 3, (4, 10, 64))
+    out_3d_int8 = qlinear.forward(x_3d)
+    assert out_3d_int8.shape == linear_forward_f32(linear, x_3d).shape == (4, 10, 128)
+
+
+def test_qlinear_memory_compression(nne, ctx):
+    linear = new_linear(nne, 23, 256, 512)
+    qlinear = nne.QLinear.from_linear(linear, ctx)
+    fp32_bytes = 256 * 512 * 4 + 512 * 4
+    assert fp32_bytes / qlinear.memory_bytes() > 3.8
+
+
+def test_qlinear_to_linear_roundtrip(nne, ctx):
+    linear = new_linear(nne, 24, 32, 64)
+    qlinear = nne.QLinear.from_linear(linear, ctx)
+    recovered = qlinear.to_linear()
+    assert recovered.in_features == 32 and recovered.out_features == 64
+    assert np.array_equal(recovered.weight.view(np.uint32),
+                          oracle.to_linear(qlinear.qweight.reshape(64, 32), qlinear.scales).view(np.uint32))
+    x = oracle.normal(24, 2, (2, 32))
+    out_q = qlinear.forward(x)
+    out_rec = linear_forward_f32(recovered, x)
+    assert np.abs(out_q - out_rec).max() < 1e-4
+
+
+def test_example16_layer(nne, ctx):
+    """examples/16_kvcache_and_int8_quantization.rs:105-146: 512 -> 1024, batch 16."""
+    linear = new_linear(nne, 25, 512, 1024)
+    q = nne.QLinear.from_linear(linear, ctx)
+    fp32_bytes = 512 * 1024 * 4 + 1024 * 4
+    assert fp32_bytes / q.memory_bytes() > 3.9
+    x = oracle.normal(25, 2, (16, 512))
+    a, b = linear_forward_f32(linear, x), q.forward(x)
+    cos = float((a * b).sum() / (np.linalg.norm(a) * np.linalg.norm(b)))
+    assert cos > 0.999
