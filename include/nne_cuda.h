@@ -68,6 +68,11 @@ NNE_API int nne_last_error(char *buf, size_t n);
  * src/gpu/layers.rs:12-16): created once, shared by every layer placed on that device.       */
 NNE_API int nne_cuda_ctx_create(int device, nne_ctx **out);
 NNE_API int nne_cuda_ctx_destroy(nne_ctx *ctx);
+/* Synchronises the device and reads the context's device error word.  Kernels here never spin
+ * without a limit: a wait that runs out (about 2 s) sets this word and the kernel returns.  Returns
+ * NNE_ERR_TIMEOUT (and clears the word) if that happened since the last check, else NNE_OK.  The
+ * `_host` entry points perform this check themselves. */
+NNE_API int nne_cuda_ctx_check(nne_ctx *ctx);
 /* Device facts the host side sizes its work with.  Any out pointer may be NULL. */
 NNE_API int nne_cuda_ctx_info(const nne_ctx *ctx, int *device, int *sm_count, int *cc_major,
                               int *cc_minor, size_t *total_mem_bytes);

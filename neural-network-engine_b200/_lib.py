@@ -23,6 +23,7 @@ SIGNATURES = {
     "nne_last_error": (C.c_int, [C.c_char_p, C.c_size_t]),
     "nne_cuda_ctx_create": (C.c_int, [C.c_int, c_void_pp]),
     "nne_cuda_ctx_destroy": (C.c_int, [C.c_void_p]),
+    "nne_cuda_ctx_check": (C.c_int, [C.c_void_p]),
     "nne_cuda_ctx_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                     C.POINTER(C.c_int), C.POINTER(C.c_int),
                                     C.POINTER(C.c_size_t)]),

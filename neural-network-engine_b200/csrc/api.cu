@@ -178,6 +178,18 @@ int nne_cuda_ctx_create(int device, nne_ctx **out) {
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
     e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->absmax_word, 256);
+    if (e == cudaSuccess) e = cudaMemset(ctx->absmax_word, 0, 256);
+    if (e == cudaSuccess) ctx->err_word = reinterpret_cast<int *>(ctx->absmax_word) + 16;
+    if (e == cudaSuccess) {
+        // Keep freed stream-ordered workspaces cached in the pool instead of returning them to
+        // the driver at every synchronisation.
+        cudaMemPool_t pool;
+        if (cudaDeviceGetDefaultMemPool(&pool, device) == cudaSuccess) {
+            uint64_t keep = ~0ull;
+            cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        }
+        cudaGetLastError();
+    }
     if (e != cudaSuccess) {
         int st = fail(NNE_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
         nne_cuda_ctx_destroy(ctx);
@@ -199,9 +211,22 @@ int nne_cuda_ctx_destroy(nne_ctx *ctx) {
     ctx->stage_a.release();
     ctx->stage_b.release();
     ctx->stage_c.release();
-    ctx->xbf16.release();
     if (ctx->absmax_word) cudaFree(ctx->absmax_word);
     delete ctx;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_cuda_ctx_check(nne_ctx *ctx) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    NNE_CUDA_TRY(cudaDeviceSynchronize());
+    int word = 0;
+    NNE_CUDA_TRY(cudaMemcpy(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (word != 0) {
+        NNE_CUDA_TRY(cudaMemset(ctx->err_word, 0, sizeof(int)));
+        return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
+    }
     return NNE_OK;
     NNE_GUARD_END
 }
@@ -529,7 +554,13 @@ int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, siz
     if (xb) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, x_host, xb, cudaMemcpyHostToDevice, s));
     NNE_TRY(forward_dev(ql, (const float *)ctx->stage_a.ptr, m, k, (float *)ctx->stage_b.ptr, ql->n, s));
     NNE_CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_b.ptr, yb, cudaMemcpyDeviceToHost, s));
+    int word = 0;
+    NNE_CUDA_TRY(cudaMemcpyAsync(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost, s));
     NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    if (word != 0) {
+        cudaMemsetAsync(ctx->err_word, 0, sizeof(int), s);
+        return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
+    }
     return NNE_OK;
     NNE_GUARD_END
 }

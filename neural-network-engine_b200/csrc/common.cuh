@@ -83,7 +83,7 @@ struct nne_ctx {
     std::mutex mu;                  // serialises *_host calls and workspace growth
     nne::GrowBuf stage_a, stage_b, stage_c;  // host-call staging (inputs / outputs)
     unsigned int *absmax_word = nullptr;     // 4-byte scratch for the per-tensor absmax
-    nne::GrowBuf xbf16;                      // bf16 copy of the activations for the tensor path
+    int *err_word = nullptr;                 // device error word: a kernel's bounded wait ran out
 };
 
 struct nne_qlinear {

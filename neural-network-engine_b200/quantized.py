@@ -72,6 +72,13 @@ class CudaContext:
             raise GpuError("context was destroyed")
         return self._h
 
+    def check(self) -> None:
+        """Synchronises the device; raises GpuError if a kernel's bounded wait ran out."""
+        try:
+            check(load().nne_cuda_ctx_check(self.handle))
+        except NneError as e:
+            raise GpuError(e.message) from e
+
     def close(self):
         if getattr(self, "_h", None) is not None:
             load().nne_cuda_ctx_destroy(self._h)
