@@ -234,7 +234,7 @@ def run_native(args):
     stream = torch.cuda.current_stream()
 
     def step():
-        s = stream.cuda_stream
+        s = torch.cuda.current_stream().cuda_stream
         for L in layers:
             st = lib.nne_qlinear_forward_dev(L["h"], L["x"].data_ptr(), 1, L["k"],
                                              L["y_own"].data_ptr(), s)
@@ -252,6 +252,21 @@ def run_native(args):
         step()
     barrier()
 
+    # One step is 12 launches of a few microseconds each: replaying it as a CUDA graph keeps the
+    # host's per-launch cost out of the device-timed region.  (N > 1 keeps eager launches: the
+    # NCCL all-gather between layers is issued by torch.distributed.)
+    graph = None
+    if world == 1 and not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        with torch.cuda.graph(graph, stream=side):
+            step()  # step() launches on torch's current stream, which is `side` here
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+
     # device-timed region: K steps back to back on one stream
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -262,10 +277,15 @@ def run_native(args):
     barrier()
     e0.record(stream)
     for _ in range(args.steps):
-        step()
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
     e1.record(stream)
     barrier()
     launches = lib.nne_launch_count() - launches0
+    if graph is not None:
+        launches = args.steps * len(layers)  # replayed kernel nodes, one per layer per step
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -325,6 +345,7 @@ def run_native(args):
                        "m": 1, "replicas_per_shape": REPLICAS, "layers_per_step": len(layers),
                        "weight_bytes_per_step_per_gpu": sum(L["n"] * L["k"] for L in layers),
                        "l2": "rotation set of distinct weights larger than the 126 MB L2",
+                       "launch": "CUDA graph replay of one step" if graph is not None else "eager",
                        "parallelism": "1 GPU" if world == 1 else
                        f"column shards over {world} GPUs + NCCL all-gather of output slices"},
             "roofline": {"bound": "hbm", "kernel": "qgemv_kernel", "achieved": achieved,
@@ -404,6 +425,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
