@@ -379,6 +379,12 @@ int nne_qlinear_create_from_f32_dev(nne_ctx *ctx, const float *w_dev, const floa
                                         cudaMemcpyDeviceToDevice, s);
         if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "bias copy failed: %s", cudaGetErrorString(e));
     }
+    // The layer is handed out only once its codes are complete: forwards may read the weights
+    // ahead of the stream's earlier work (programmatic dependent launch).
+    if (st == NNE_OK) {
+        cudaError_t e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "quantize failed: %s", cudaGetErrorString(e));
+    }
     if (st == NNE_OK) st = prefill_prepare_layer(ql);
     if (st != NNE_OK) {
         nne_qlinear_destroy(ql);

@@ -118,6 +118,10 @@ bool gemv_supports(size_t n, size_t k, size_t m);
 int launch_gemv(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                 const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                 cudaStream_t s);
+bool gemv_tma_supports(size_t n, size_t k, size_t m);  // m = rows of one launch, 1..4
+int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
+                    const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
+                    cudaStream_t s);
 int launch_generic(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                    const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                    cudaStream_t s);

@@ -11,6 +11,8 @@
 // 16-byte chunks c = t + i*T (i < I) of every row, so its slice of x never changes and stays in
 // registers (I*16 floats per activation row).  int8 -> f32 is exact, accumulation is fp32 FMA,
 // scale and bias are applied as a separate multiply and add like the reference (:187-190).
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace nne {
@@ -295,24 +297,38 @@ int launch_gemv(nne_ctx *ctx, const int8_t *q, const float *scales, const float 
                 const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                 cudaStream_t s) {
     // Activation rows go through in blocks of at most 4; each block streams the weights once.
+    // A block goes to the TMA-staged kernel when its slice of x fits in registers there,
+    // otherwise to the register-staged kernel in this file.
+    static const bool no_tma = [] {
+        const char *e = getenv("NNE_NO_TMA_GEMV");
+        return e && e[0] == '1';
+    }();
     size_t r = 0;
     while (r < m) {
         const size_t left = m - r;
+        size_t mt = left >= 4 ? 4 : left;
         const float *xb = x + r * k;
         float *yb = y + r * ldy;
-        if (left >= 4) {
+        if (!no_tma) {
+            // prefer the largest block the TMA kernel takes, down to 1
+            size_t t = mt;
+            while (t >= 1 && !gemv_tma_supports(n, k, t)) --t;
+            if (t >= 1 && (t == mt || t >= 2 || mt == 1)) {
+                NNE_TRY(launch_gemv_tma(ctx, q, scales, bias, xb, yb, n, k, t, ldy, s));
+                r += t;
+                continue;
+            }
+        }
+        if (mt == 4) {
             NNE_TRY(launch_mt<4>(ctx, q, scales, bias, xb, yb, n, k, ldy, s));
-            r += 4;
-        } else if (left == 3) {
+        } else if (mt == 3) {
             NNE_TRY(launch_mt<3>(ctx, q, scales, bias, xb, yb, n, k, ldy, s));
-            r += 3;
-        } else if (left == 2) {
+        } else if (mt == 2) {
             NNE_TRY(launch_mt<2>(ctx, q, scales, bias, xb, yb, n, k, ldy, s));
-            r += 2;
         } else {
             NNE_TRY(launch_mt<1>(ctx, q, scales, bias, xb, yb, n, k, ldy, s));
-            r += 1;
         }
+        r += mt;
     }
     return NNE_OK;
 }
