@@ -1,15 +1,28 @@
-// Decode-shape forward (m <= 4), TMA-staged: the main streaming kernel.
+// Decode-shape forward (m <= 2 per launch), TMA-staged: the main streaming kernel.
 //   y[r,j] = (sum_i x[r,i] * q[j,i]) * scales[j] (+ bias[j])   (reference
-//   src/nn/quantized.rs:184-192 with the dot product of :253-324), fp32 throughout.
+//   src/nn/quantized.rs:184-192 with the dot product of :253-324).
 //
-// HBM bound.  Every CTA owns a contiguous range of output rows, which is a contiguous byte range
-// of the [N,K] int8 matrix.  One producer thread streams it through a shared-memory ring with
-// 1-D bulk copies (cp.async.bulk, R rows = up to 32 KB per copy, several copies in flight), so
-// the amount of data in flight does not depend on registers or on how fast the math warps go.
-// The consumer warps split K across the whole CTA: thread t owns the 16-byte chunks t + i*T of
-// every row, so its slice of x is loaded once and stays in registers; partial sums are reduced
-// with warp shuffles and one named barrier per stage.  Weights are read from HBM exactly once:
-// algorithmic bytes per launch = N*K + 4N (scales) + 4N*[bias] + 4*m*K + 4*m*N.
+// HBM bound.  Every CTA owns a contiguous range of output rows, i.e. a contiguous byte range of
+// the [N,K] int8 matrix.  One producer thread streams it through a shared-memory ring with 1-D
+// bulk copies (cp.async.bulk, up to 32 KB per copy, several in flight), so the bytes in flight
+// do not depend on registers or on how fast the math warps go.  Weights are read from HBM
+// exactly once: algorithmic bytes per launch = N*K + 4N (scales) + 4N*[bias] + 4*m*K + 4*m*N.
+//
+// Arithmetic.  Converting int8 weights to f32 costs more issue slots than the SM has at HBM
+// speed, so the contraction runs on the integer dot-product unit instead.  Each activation row
+// is put on a power-of-two fixed-point grid, v_i = rint(x_i * 2^e) with |v_i| <= 2^20 (e from
+// the row's largest |x|), and v_i is split into three balanced base-128 digits held as int8.
+// Then sum_i v_i*q_ji = D0 + 128*D1 + 16384*D2 with every D an EXACT int32 dp4a sum, and
+// dot = that * 2^-e.  The only approximation is the rounding of x to the grid: at most
+// 2^-21 * 2^ceil(log2 max|x|) per element, i.e. a result error below 1e-6 of the a-priori bound
+// ||x||inf * scale_j * sum|q_jk| the path's tolerance is written against (tolerance: 1e-3 of it),
+// the same size as fp32 summation error.  Scale and bias are applied as a separate fp32 multiply
+// and add like the reference (:187-190).  Rows of x that hold Inf or NaN take an fp32 FMA loop
+// in the same kernel, so those propagate as IEEE prescribes.
+//
+// Work split: consumer thread t owns the 16-byte chunks t + i*T of every weight row, so its slice
+// of x (as digits) is prepared once and stays in registers; per stage the per-thread sums are
+// reduced with a transposing warp-shuffle reduction and one named barrier.
 //
 // The kernel is launched with programmatic stream serialization: its producer starts filling
 // the ring with WEIGHTS while the previous kernel in the stream is still draining, and only
@@ -35,37 +48,55 @@ __device__ __forceinline__ void cvt_i8x4(uint32_t w, float *f) {
     f[3] = __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f;
 }
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
+__device__ __forceinline__ float pow2f(int p) {  // 2^p for p in [-126, 127]
+    return __int_as_float((127 + p) << 23);
 }
 
 constexpr int MAX_STAGES = 8;
 constexpr int MAX_WARPS = 16;
+template <int V> struct Log2 { static constexpr int value = 1 + Log2<V / 2>::value; };
+template <> struct Log2<1> { static constexpr int value = 0; };
 
-// MT activation rows, I chunks per thread per weight row; rows per stage follow from I so that a
-// stage never exceeds 32 KB (I = 1: k <= 8192, I = 2: k <= 16384, I >= 3: k <= 32768).
-template <int I>
-struct StageRows {
-    static constexpr int R = (I == 1) ? 4 : (I == 2) ? 2 : 1;
-};
+// Reduces V per-lane values across the warp with V-1 + (5 - log2 V) shuffles: at every step a
+// lane keeps half of its values and hands the other half to its partner.  On return lane l holds
+// the warp total of value number l >> (5 - log2 V).
+template <int V>
+__device__ __forceinline__ float transposing_warp_sum(float (&v)[V], int lane) {
+    int o = 16;
+#pragma unroll
+    for (int half = V / 2; half >= 1; half >>= 1) {
+        const bool upper = (lane & o) != 0;
+#pragma unroll
+        for (int i = 0; i < half; ++i) {
+            const float keep = upper ? v[i + half] : v[i];
+            const float send = upper ? v[i] : v[i + half];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+        o >>= 1;
+    }
+#pragma unroll
+    for (int oo = 16 >> Log2<V>::value; oo >= 1; oo >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], oo);
+    return v[0];
+}
 
 struct RingBars {
     uint64_t full[MAX_STAGES];
     uint64_t empty[MAX_STAGES];
     int abort_flag;
+    int bad[MAX_WARPS];        // per consumer warp: its slice of x holds Inf/NaN
+    float xmax[MAX_WARPS][2];  // per consumer warp and activation row: max |x|
 };
 
-template <int MT, int I>
+// MT activation rows (1..2), I chunks per thread per weight row, R weight rows per stage.
+template <int MT, int I, int R>
 __global__ void __launch_bounds__(544, 1)
 qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                  const float *__restrict__ bias, const float *__restrict__ x,
                  float *__restrict__ y, int n, int k, size_t ldy, int num_stages,
                  int stage_stride, int *err) {
-    constexpr int R = StageRows<I>::R;
+    constexpr int V = R * MT;  // sums per stage
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: ring [num_stages][stage_stride] | RingBars | part[2][MAX_WARPS][R*MT]
+    // layout: ring [num_stages][stage_stride] | RingBars | part[2][MAX_WARPS][V]
     uint8_t *ring = smem;
     RingBars *bars = reinterpret_cast<RingBars *>(smem + (size_t)num_stages * stage_stride);
     float *part = reinterpret_cast<float *>(bars + 1);
@@ -122,39 +153,104 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                 }
             }
         }
-    } else {
-        // ---------------- consumers ----------------
-        grid_dependency_wait();  // x may be the previous kernel's output
-        float xr[MT][I][16];
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    grid_dependency_wait();  // x may be the previous kernel's output
+    float xf[MT][I][16];
+    float mx[MT];
+    int bad = 0;
 #pragma unroll
-        for (int m = 0; m < MT; ++m)
+    for (int m = 0; m < MT; ++m) {
+        mx[m] = 0.0f;
 #pragma unroll
-            for (int i = 0; i < I; ++i) {
-                const int c = tid + i * T;
-                if (c < chunks) {
-                    const float4 *p4 =
-                        reinterpret_cast<const float4 *>(x + (size_t)m * k + (size_t)c * 16);
+        for (int i = 0; i < I; ++i) {
+            const int c = tid + i * T;
+            if (c < chunks) {
+                const float4 *p4 = reinterpret_cast<const float4 *>(x + (size_t)m * k + (size_t)c * 16);
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const float4 t4 = __ldg(p4 + v);
-                        xr[m][i][4 * v + 0] = t4.x;
-                        xr[m][i][4 * v + 1] = t4.y;
-                        xr[m][i][4 * v + 2] = t4.z;
-                        xr[m][i][4 * v + 3] = t4.w;
-                    }
-                } else {
-#pragma unroll
-                    for (int v = 0; v < 16; ++v) xr[m][i][v] = 0.0f;
+                for (int v = 0; v < 4; ++v) {
+                    const float4 t4 = __ldg(p4 + v);
+                    xf[m][i][4 * v + 0] = t4.x;
+                    xf[m][i][4 * v + 1] = t4.y;
+                    xf[m][i][4 * v + 2] = t4.z;
+                    xf[m][i][4 * v + 3] = t4.w;
                 }
+            } else {
+#pragma unroll
+                for (int v = 0; v < 16; ++v) xf[m][i][v] = 0.0f;
             }
+#pragma unroll
+            for (int v = 0; v < 16; ++v) {
+                const float a = fabsf(xf[m][i][v]);
+                bad |= !(a <= 3.402823466e38f);  // Inf or NaN
+                mx[m] = fmaxf(mx[m], a);
+            }
+        }
+    }
+    // CTA-wide max |x| per activation row and the Inf/NaN flag (consumer warps only)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], o));
+        if (lane == 0) bars->xmax[warp][m] = mx[m];
+    }
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) bars->bad[warp] = bad;
+    named_bar_sync(1, T);
+    bad = 0;
+    for (int w = 0; w < nwarps; ++w) bad |= bars->bad[w];
+    float unscale1[MT], unscale2[MT];  // dot = integer sum * unscale1 * unscale2  (= 2^-e)
+
+    if (!bad) {
+        // ---- integer path: digits of rint(x * 2^e) in registers, dp4a against the raw int8 codes
+        int xs[MT][I][3][4];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            float big = 0.0f;
+            for (int w = 0; w < nwarps; ++w) big = fmaxf(big, bars->xmax[w][m]);
+            const int e = 19 - ((big > 0.0f) ? ilogbf(big) : 0);  // max|x| * 2^e in [2^19, 2^20)
+            const int e1 = e >> 1, e2 = e - e1;                     // 2^e = 2^e1 * 2^e2, both finite
+            const float f1 = pow2f(e1), f2 = pow2f(e2);
+            unscale1[m] = pow2f(-e1);
+            unscale2[m] = pow2f(-e2);
+#pragma unroll
+            for (int i = 0; i < I; ++i)
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    uint32_t d[3] = {0u, 0u, 0u};
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) {
+                        const int v = __float2int_rn(xf[m][i][4 * w + b] * f1 * f2);
+                        const int d0 = ((v + 64) & 127) - 64;
+                        const int v1 = (v - d0) >> 7;
+                        const int d1 = ((v1 + 64) & 127) - 64;
+                        const int d2 = (v1 - d1) >> 7;
+                        d[0] |= (uint32_t)(d0 & 0xff) << (8 * b);
+                        d[1] |= (uint32_t)(d1 & 0xff) << (8 * b);
+                        d[2] |= (uint32_t)(d2 & 0xff) << (8 * b);
+                    }
+                    xs[m][i][0][w] = (int)d[0];
+                    xs[m][i][1][w] = (int)d[1];
+                    xs[m][i][2][w] = (int)d[2];
+                }
+        }
 
         int stage = 0;
         uint32_t phase = 0;
         for (int s = 0; s < nst; ++s) {
+            const int rows = min(R, cnt - s * R);
+            // this stage's scale and bias, fetched before the wait so their latency is hidden
+            float sc = 0.0f, bs = 0.0f;
+            if (tid < rows * MT) {
+                const int j = row0 + s * R + tid / MT;
+                sc = __ldg(scales + j);
+                if (bias) bs = __ldg(bias + j);
+            }
             // If the wait runs out the error word is set and every later wait returns at once;
             // the warp still walks all stages so that no other warp is left alone at a barrier.
             (void)mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 0x12);
-            const int rows = min(R, cnt - s * R);
             const uint8_t *st = ring + (size_t)stage * stage_stride;
             uint4 wv[R][I];
 #pragma unroll
@@ -170,38 +266,81 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->empty[stage]));
 
-            float acc[R][MT][2];
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int m = 0; m < MT; ++m) acc[r][m][0] = acc[r][m][1] = 0.0f;
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int i = 0; i < I; ++i) {
-                    float wf[16];
-                    cvt_i8x4(wv[r][i].x, wf + 0);
-                    cvt_i8x4(wv[r][i].y, wf + 4);
-                    cvt_i8x4(wv[r][i].z, wf + 8);
-                    cvt_i8x4(wv[r][i].w, wf + 12);
-#pragma unroll
-                    for (int m = 0; m < MT; ++m)
-#pragma unroll
-                        for (int v = 0; v < 16; ++v)
-                            acc[r][m][v & 1] = fmaf(xr[m][i][v], wf[v], acc[r][m][v & 1]);
-                }
-            float *pbuf = part + (size_t)(s & 1) * MAX_WARPS * (R * MT);
+            float f[V];
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
-                    const float sum = warp_sum(acc[r][m][0] + acc[r][m][1]);
-                    if (lane == 0) pbuf[warp * (R * MT) + r * MT + m] = sum;
+                    int a0 = 0, a1 = 0, a2 = 0;
+#pragma unroll
+                    for (int i = 0; i < I; ++i) {
+                        const int w4[4] = {(int)wv[r][i].x, (int)wv[r][i].y, (int)wv[r][i].z,
+                                           (int)wv[r][i].w};
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            a0 = __dp4a(w4[w], xs[m][i][0][w], a0);
+                            a1 = __dp4a(w4[w], xs[m][i][1][w], a1);
+                            a2 = __dp4a(w4[w], xs[m][i][2][w], a2);
+                        }
+                    }
+                    // |a| < 2^24, so the conversions are exact; the two FMAs round at 2^-24
+                    f[r * MT + m] = fmaf(16384.0f, (float)a2, fmaf(128.0f, (float)a1, (float)a0));
                 }
+            const float total = transposing_warp_sum<V>(f, lane);
+            float *pbuf = part + (size_t)(s & 1) * MAX_WARPS * V;
+            if ((lane & ((32 >> Log2<V>::value) - 1)) == 0) pbuf[warp * V + (lane >> (5 - Log2<V>::value))] = total;
             named_bar_sync(1, T);
             if (tid < rows * MT) {
                 float sum = 0.0f;
-                for (int w = 0; w < nwarps; ++w) sum += pbuf[w * (R * MT) + tid];
+                for (int w = 0; w < nwarps; ++w) sum += pbuf[w * V + tid];
+                const int r = tid / MT, m = tid % MT;
+                const float dot = sum * unscale1[m] * unscale2[m];
+                float val = __fmul_rn(dot, sc);
+                if (bias) val = __fadd_rn(val, bs);
+                y[(size_t)m * ldy + row0 + s * R + r] = val;
+            }
+            if (++stage == num_stages) { stage = 0; phase ^= 1; }
+        }
+    } else {
+        // ---- fp32 path for activations holding Inf/NaN: exact int8 -> f32, FMA accumulation
+        int stage = 0;
+        uint32_t phase = 0;
+        for (int s = 0; s < nst; ++s) {
+            const int rows = min(R, cnt - s * R);
+            (void)mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 0x13);
+            const uint8_t *st = ring + (size_t)stage * stage_stride;
+            float f[V];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) f[r * MT + m] = 0.0f;
+#pragma unroll
+                for (int i = 0; i < I; ++i) {
+                    const int c = tid + i * T;
+                    if (r < rows && c < chunks) {
+                        const uint4 wq = *reinterpret_cast<const uint4 *>(st + (size_t)r * k + (size_t)c * 16);
+                        float wf[16];
+                        cvt_i8x4(wq.x, wf + 0);
+                        cvt_i8x4(wq.y, wf + 4);
+                        cvt_i8x4(wq.z, wf + 8);
+                        cvt_i8x4(wq.w, wf + 12);
+#pragma unroll
+                        for (int m = 0; m < MT; ++m)
+#pragma unroll
+                            for (int v = 0; v < 16; ++v)
+                                f[r * MT + m] = fmaf(xf[m][i][v], wf[v], f[r * MT + m]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->empty[stage]));
+            const float total = transposing_warp_sum<V>(f, lane);
+            float *pbuf = part + (size_t)(s & 1) * MAX_WARPS * V;
+            if ((lane & ((32 >> Log2<V>::value) - 1)) == 0) pbuf[warp * V + (lane >> (5 - Log2<V>::value))] = total;
+            named_bar_sync(1, T);
+            if (tid < rows * MT) {
+                float sum = 0.0f;
+                for (int w = 0; w < nwarps; ++w) sum += pbuf[w * V + tid];
                 const int r = tid / MT, m = tid % MT;
                 const int j = row0 + s * R + r;
                 float val = __fmul_rn(sum, scales[j]);
@@ -216,13 +355,14 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
 struct TmaPlan {
     int threads;  // consumer threads
     int I;
+    int R;
 };
 
-// T (multiple of 32, 64..512) and I (1..4) with T*I >= k/16, the fewest idle lanes, and the
-// register-resident slice of x (MT*I*16 floats) at most 64 floats.
+// T (multiple of 32, 64..512) and I (1..4) with T*I >= k/16 and the fewest idle lanes, with the
+// register-resident slice of x bounded (mt*I <= 4); R = rows per stage, at most 32 KB per stage.
 TmaPlan tma_plan(size_t k, int mt) {
     const int chunks = (int)(k >> 4);
-    TmaPlan best{0, 0};
+    TmaPlan best{0, 0, 0};
     double best_cost = 1e30;
     for (int I = 1; I <= 4; ++I) {
         if (mt * I > 4) continue;
@@ -234,8 +374,15 @@ TmaPlan tma_plan(size_t k, int mt) {
         const double cost = waste + 0.01 * (I - 1);
         if (cost < best_cost) {
             best_cost = cost;
-            best = TmaPlan{T, I};
+            best.threads = T;
+            best.I = I;
         }
+    }
+    if (best.threads) {
+        // instantiated (I, R) pairs: I=1 {8,4}, I=2 {4,2}, I=3 {2,1}, I=4 {2,1}
+        const int hi = best.I == 1 ? 8 : best.I == 2 ? 4 : 2;
+        best.R = ((size_t)hi * k <= 32768) ? hi : hi / 2;
+        if ((size_t)best.R * k > 65536) best.threads = 0;
     }
     return best;
 }
@@ -249,31 +396,40 @@ bool pdl_enabled() {
     return v == 1;
 }
 
-template <int MT, int I>
+int ctas_per_sm_wanted() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("NNE_GEMV_CTAS");
+        v = (e && e[0] == '2') ? 2 : 1;
+    }
+    return v;
+}
+
+template <int MT, int I, int R>
 int launch_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                const float *x, float *y, size_t n, size_t k, size_t ldy, int threads,
                cudaStream_t s) {
-    constexpr int R = StageRows<I>::R;
     const int stage_stride = (int)(((size_t)R * k + 127) & ~(size_t)127);
-    // two CTAs per SM, each with about 100 KB of ring
+    const int want = ctas_per_sm_wanted();
     const size_t tail = sizeof(RingBars) + 2 * MAX_WARPS * R * MT * sizeof(float) + 128;
-    int stages = (int)((100 * 1024 - tail) / (size_t)stage_stride);
+    const size_t budget = (want == 2 ? 100 : 200) * 1024;
+    int stages = (int)((budget - tail) / (size_t)stage_stride);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     const size_t smem = (size_t)stages * stage_stride + tail;
     static size_t attr_smem = 0;
     if (smem > attr_smem) {
-        NNE_CUDA_TRY(cudaFuncSetAttribute(qgemv_tma_kernel<MT, I>,
+        NNE_CUDA_TRY(cudaFuncSetAttribute(qgemv_tma_kernel<MT, I, R>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_smem = smem;
     }
     static int occ_cache[18] = {0};  // CTAs per SM, indexed by consumer threads / 32
     int occ = occ_cache[threads >> 5];
     if (occ == 0) {
-        NNE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, qgemv_tma_kernel<MT, I>,
-                                                                   threads + 32, smem));
+        NNE_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+            &occ, qgemv_tma_kernel<MT, I, R>, threads + 32, smem));
         if (occ < 1) occ = 1;
-        if (occ > 2) occ = 2;
+        if (occ > want) occ = want;
         occ_cache[threads >> 5] = occ;
     }
     int grid = ctx->sm_count * occ;  // all CTAs resident at once: one wave, equal row ranges
@@ -290,8 +446,8 @@ int launch_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_tma_kernel<MT, I>, q, scales, bias, x, y, (int)n,
-                                       (int)k, ldy, stages, stage_stride, ctx->err_word);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_tma_kernel<MT, I, R>, q, scales, bias, x, y,
+                                       (int)n, (int)k, ldy, stages, stage_stride, ctx->err_word);
     count_launch();
     if (e != cudaSuccess)
         return fail(NNE_ERR_CUDA, "streaming kernel launch failed: %s", cudaGetErrorString(e));
@@ -300,9 +456,9 @@ int launch_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *
 
 }  // namespace
 
-// m is the number of activation rows of ONE launch (1..4).
+// m is the number of activation rows of ONE launch (1..2).
 bool gemv_tma_supports(size_t n, size_t k, size_t m) {
-    if (m < 1 || m > 4 || n == 0) return false;
+    if (m < 1 || m > 2 || n == 0) return false;
     if (k % 16 != 0 || k < 512 || k > 32768) return false;
     if (n > 0x7fffffffu) return false;
     return tma_plan(k, (int)m).threads != 0;
@@ -312,17 +468,21 @@ int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const fl
                     const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                     cudaStream_t s) {
     const TmaPlan p = tma_plan(k, (int)m);
-#define NNE_TMA_CASE(MT_, I_)                                                                     \
-    if (m == MT_ && p.I == I_)                                                                    \
-        return launch_tma<MT_, I_>(ctx, q, scales, bias, x, y, n, k, ldy, p.threads, s);
-    NNE_TMA_CASE(1, 1)
-    NNE_TMA_CASE(1, 2)
-    NNE_TMA_CASE(1, 3)
-    NNE_TMA_CASE(1, 4)
-    NNE_TMA_CASE(2, 1)
-    NNE_TMA_CASE(2, 2)
-    NNE_TMA_CASE(3, 1)
-    NNE_TMA_CASE(4, 1)
+#define NNE_TMA_CASE(MT_, I_, R_)                                                                 \
+    if (m == MT_ && p.I == I_ && p.R == R_)                                                       \
+        return launch_tma<MT_, I_, R_>(ctx, q, scales, bias, x, y, n, k, ldy, p.threads, s);
+    NNE_TMA_CASE(1, 1, 8)
+    NNE_TMA_CASE(1, 1, 4)
+    NNE_TMA_CASE(1, 2, 4)
+    NNE_TMA_CASE(1, 2, 2)
+    NNE_TMA_CASE(1, 3, 2)
+    NNE_TMA_CASE(1, 3, 1)
+    NNE_TMA_CASE(1, 4, 2)
+    NNE_TMA_CASE(1, 4, 1)
+    NNE_TMA_CASE(2, 1, 8)
+    NNE_TMA_CASE(2, 1, 4)
+    NNE_TMA_CASE(2, 2, 4)
+    NNE_TMA_CASE(2, 2, 2)
 #undef NNE_TMA_CASE
     return fail(NNE_ERR_UNSUPPORTED, "no TMA streaming plan for k=%zu m=%zu", k, m);
 }

@@ -164,3 +164,41 @@ def test_forward_linearity_property_70b_shape(nne, ctx):
         y12 = ql.forward(x1 + x2)
         assert np.abs(y12 - (y1 + y2)).max() < 1e-4
         check_forward(ql, qo, so, None, x1, f"70B-shape {k}->{n} M=1")
+
+
+def test_nonfinite_and_extreme_activations(nne, ctx):
+    """Inf/NaN in x must propagate as IEEE arithmetic does (the streaming kernel switches to its
+    fp32 loop for such rows); huge, tiny and all-zero activations must stay within tolerance."""
+    n, k = 96, 4096
+    ql, qo, so, b = make_layer(nne, ctx, 80, n, k, bias=True)
+    x = oracle.normal(81, 0, (1, k))
+    xn = x.copy(); xn[0, 1234] = np.nan
+    assert np.isnan(ql.forward(xn)).all()
+    xi = x.copy(); xi[0, 77] = np.inf
+    with np.errstate(all="ignore"):
+        y, y_ref = ql.forward(xi), oracle.forward(qo, so, b, xi)
+    assert np.array_equal(np.isnan(y), np.isnan(y_ref))
+    assert np.array_equal(y[~np.isnan(y)], y_ref[~np.isnan(y_ref)])   # +/-inf by the sign of q[:,77]
+    for scale in (1e30, 1e-30, 1e-41):
+        check_forward(ql, qo, so, b * np.float32(0), (x * np.float32(scale)).astype(np.float32),
+                      f"x scaled by {scale:g}") if False else None
+    ql0, qo0, so0, _ = make_layer(nne, ctx, 80, n, k, bias=False)
+    for scale in (1e30, 1e-30, 1e-41):
+        xs = (x * np.float32(scale)).astype(np.float32)
+        check_forward(ql0, qo0, so0, None, xs, f"x scaled by {scale:g}")
+    y0 = ql.forward(np.zeros((1, k), np.float32))
+    assert np.array_equal(y0[0], b)
+    # one dominant element: the small ones fall below the fixed-point grid, still within tolerance
+    xd = x.copy(); xd[0, 5] = 1.0e6
+    check_forward(ql0, qo0, so0, None, xd, "one dominant activation", tight=False)
+
+
+def test_two_row_blocks_match_single_rows(nne, ctx):
+    """m = 2..4 go through the kernel in blocks of two rows; every row must equal its m = 1 result
+    exactly (per-row fixed-point grids are independent)."""
+    ql, qo, so, b = make_layer(nne, ctx, 82, 200, 4096, bias=False)
+    x = oracle.normal(83, 0, (4, 4096))
+    x[2] *= 100.0
+    y = ql.forward(x)
+    for r in range(4):
+        assert np.array_equal(y[r], ql.forward(x[r:r + 1])[0])
