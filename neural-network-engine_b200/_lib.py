@@ -9,7 +9,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libnne_cuda.so")
+# NNE_CUDA_LIB points the loader at another build of the same library (e.g. one with tracing).
+LIB_PATH = os.environ.get("NNE_CUDA_LIB") or os.path.join(_HERE, "lib", "libnne_cuda.so")
 
 OK, INVALID_ARGUMENT, SHAPE_MISMATCH, CUDA, NCCL, TIMEOUT, OUT_OF_MEMORY, UNSUPPORTED = range(8)
 

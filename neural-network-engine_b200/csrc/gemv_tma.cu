@@ -79,6 +79,19 @@ __device__ __forceinline__ float transposing_warp_sum(float (&v)[V], int lane) {
     return v[0];
 }
 
+#ifdef NNE_TRACE
+// Debug builds only: per-CTA timestamps (globaltimer ns) of the kernel's phases.
+__device__ unsigned long long g_trace[1024 * 16];
+#define NNE_TRACE_MARK(slot)                                                  \
+    do {                                                                      \
+        if (blockIdx.x < 1024) g_trace[blockIdx.x * 16 + (slot)] = globaltimer_ns(); \
+    } while (0)
+#else
+#define NNE_TRACE_MARK(slot) \
+    do {                     \
+    } while (0)
+#endif
+
 struct RingBars {
     uint64_t full[MAX_STAGES];
     uint64_t empty[MAX_STAGES];
@@ -93,13 +106,16 @@ __global__ void __launch_bounds__(544, 1)
 qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
                  const float *__restrict__ bias, const float *__restrict__ x,
                  float *__restrict__ y, int n, int k, size_t ldy, int num_stages,
-                 int stage_stride, int *err) {
+                 int stage_stride, int sb_rows, int l2_prefetch, int *err) {
     constexpr int V = R * MT;  // sums per stage
     extern __shared__ __align__(128) uint8_t smem[];
-    // layout: ring [num_stages][stage_stride] | RingBars | part[2][MAX_WARPS][V]
+    // layout: ring [num_stages][stage_stride] | RingBars | part[2][MAX_WARPS][V] |
+    //         scale_s[sb_rows] | bias_s[sb_rows]   (this CTA's rows; sb_rows = 0: read from global)
     uint8_t *ring = smem;
     RingBars *bars = reinterpret_cast<RingBars *>(smem + (size_t)num_stages * stage_stride);
     float *part = reinterpret_cast<float *>(bars + 1);
+    float *scale_s = part + 2 * MAX_WARPS * V;
+    float *bias_s = scale_s + sb_rows;
 
     const int T = blockDim.x - 32;  // consumer threads; the last warp is the producer
     const int tid = threadIdx.x;
@@ -132,17 +148,32 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int s = 0; s < nst; ++s) {
+            NNE_TRACE_MARK(8);
+            // Pull this CTA's whole byte range towards L2 right away: the DRAM stream then runs at
+            // full depth from the first cycle (and, under programmatic dependent launch, already
+            // while the previous kernel drains), independent of how small the shared ring is.
+            const uint64_t pol_stream = l2_policy_evict_first();
+            if (l2_prefetch) {
+                const uint8_t *base = reinterpret_cast<const uint8_t *>(q) + (size_t)row0 * k;
+                const size_t total = (size_t)cnt * k;
+                for (size_t off = 0; off < total; off += 32768) {
+                    const size_t left = total - off;
+                    bulk_prefetch_l2(base + off, (uint32_t)(left < 32768 ? left : 32768), pol_stream);
+                }
+            }
+            for (int s = 0; s < nst && ok; ++s) {
                 ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, err, 0x11);
                 if (!ok) break;
+                if (s == num_stages) NNE_TRACE_MARK(9);
                 const int rows = min(R, cnt - s * R);
                 const uint32_t bytes = (uint32_t)rows * (uint32_t)k;
                 const uint32_t full = smem_u32(&bars->full[stage]);
                 mbar_arrive_expect_tx(full, bytes);
-                bulk_load_1d(smem_u32(ring + (size_t)stage * stage_stride),
-                             q + (size_t)(row0 + s * R) * k, bytes, full);
+                bulk_load_1d_hint(smem_u32(ring + (size_t)stage * stage_stride),
+                                  q + (size_t)(row0 + s * R) * k, bytes, full, pol_stream);
                 if (++stage == num_stages) { stage = 0; phase ^= 1; }
             }
+            NNE_TRACE_MARK(10);
             if (!ok) {
                 for (int s = 0; s < num_stages; ++s) {
                     const unsigned long long t0 = globaltimer_ns();
@@ -157,8 +188,38 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
     }
 
     // ---------------- consumers ----------------
+    if (tid == 0) NNE_TRACE_MARK(0);
+    // Scales and bias are layer constants: fetch this CTA's rows before waiting for the previous
+    // kernel.  Loads are unconditional from clamped addresses and masked afterwards, so no
+    // predicated register write has to wait for a load that is still in flight.
+    const uint64_t pol_keep = l2_policy_evict_last();  // activations and scales stay in L2
+    float sc_pre[4], bs_pre[4];  // rows tid, tid+T, ... of this CTA (at most 4 per thread)
+    if (sb_rows) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = min(tid + u * T, cnt - 1);
+            sc_pre[u] = ldg_f1_hint(scales + row0 + i, pol_keep);
+            bs_pre[u] = bias ? ldg_f1_hint(bias + row0 + i, pol_keep) : 0.0f;
+        }
+    }
     grid_dependency_wait();  // x may be the previous kernel's output
+    if (tid == 0) NNE_TRACE_MARK(1);
     float xf[MT][I][16];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int i = 0; i < I; ++i) {
+            const int c = min(tid + i * T, chunks - 1);
+            const float4 *p4 = reinterpret_cast<const float4 *>(x + (size_t)m * k + (size_t)c * 16);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const float4 t4 = ldg_f4_hint(p4 + v, pol_keep);
+                xf[m][i][4 * v + 0] = t4.x;
+                xf[m][i][4 * v + 1] = t4.y;
+                xf[m][i][4 * v + 2] = t4.z;
+                xf[m][i][4 * v + 3] = t4.w;
+            }
+        }
     float mx[MT];
     int bad = 0;
 #pragma unroll
@@ -166,23 +227,10 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
         mx[m] = 0.0f;
 #pragma unroll
         for (int i = 0; i < I; ++i) {
-            const int c = tid + i * T;
-            if (c < chunks) {
-                const float4 *p4 = reinterpret_cast<const float4 *>(x + (size_t)m * k + (size_t)c * 16);
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const float4 t4 = __ldg(p4 + v);
-                    xf[m][i][4 * v + 0] = t4.x;
-                    xf[m][i][4 * v + 1] = t4.y;
-                    xf[m][i][4 * v + 2] = t4.z;
-                    xf[m][i][4 * v + 3] = t4.w;
-                }
-            } else {
-#pragma unroll
-                for (int v = 0; v < 16; ++v) xf[m][i][v] = 0.0f;
-            }
+            const bool live = (tid + i * T) < chunks;
 #pragma unroll
             for (int v = 0; v < 16; ++v) {
+                if (!live) xf[m][i][v] = 0.0f;
                 const float a = fabsf(xf[m][i][v]);
                 bad |= !(a <= 3.402823466e38f);  // Inf or NaN
                 mx[m] = fmaxf(mx[m], a);
@@ -198,7 +246,18 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
     }
     bad = __any_sync(0xffffffffu, bad);
     if (lane == 0) bars->bad[warp] = bad;
+    if (sb_rows) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = tid + u * T;
+            if (i < cnt) {
+                scale_s[i] = sc_pre[u];
+                bias_s[i] = bs_pre[u];
+            }
+        }
+    }
     named_bar_sync(1, T);
+    if (tid == 0) NNE_TRACE_MARK(2);
     bad = 0;
     for (int w = 0; w < nwarps; ++w) bad |= bars->bad[w];
     float unscale1[MT], unscale2[MT];  // dot = integer sum * unscale1 * unscale2  (= 2^-e)
@@ -239,18 +298,26 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
 
         int stage = 0;
         uint32_t phase = 0;
+        if (tid == 0) NNE_TRACE_MARK(3);
         for (int s = 0; s < nst; ++s) {
             const int rows = min(R, cnt - s * R);
-            // this stage's scale and bias, fetched before the wait so their latency is hidden
             float sc = 0.0f, bs = 0.0f;
             if (tid < rows * MT) {
-                const int j = row0 + s * R + tid / MT;
-                sc = __ldg(scales + j);
-                if (bias) bs = __ldg(bias + j);
+                const int jl = s * R + tid / MT;
+                if (sb_rows) {
+                    sc = scale_s[jl];
+                    bs = bias_s[jl];
+                } else {
+                    sc = __ldg(scales + row0 + jl);
+                    if (bias) bs = __ldg(bias + row0 + jl);
+                }
             }
             // If the wait runs out the error word is set and every later wait returns at once;
             // the warp still walks all stages so that no other warp is left alone at a barrier.
             (void)mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 0x12);
+            if (tid == 0 && s == 0) NNE_TRACE_MARK(4);
+            if (tid == 0 && s == 1) NNE_TRACE_MARK(5);
+            if (tid == 0 && s == nst - 1) NNE_TRACE_MARK(6);
             const uint8_t *st = ring + (size_t)stage * stage_stride;
             uint4 wv[R][I];
 #pragma unroll
@@ -301,6 +368,7 @@ qgemv_tma_kernel(const int8_t *__restrict__ q, const float *__restrict__ scales,
             }
             if (++stage == num_stages) { stage = 0; phase ^= 1; }
         }
+        if (tid == 0) NNE_TRACE_MARK(7);
     } else {
         // ---- fp32 path for activations holding Inf/NaN: exact int8 -> f32, FMA accumulation
         int stage = 0;
@@ -381,8 +449,8 @@ TmaPlan tma_plan(size_t k, int mt) {
     if (best.threads) {
         // instantiated (I, R) pairs: I=1 {8,4}, I=2 {4,2}, I=3 {2,1}, I=4 {2,1}
         const int hi = best.I == 1 ? 8 : best.I == 2 ? 4 : 2;
-        best.R = ((size_t)hi * k <= 32768) ? hi : hi / 2;
-        if ((size_t)best.R * k > 65536) best.threads = 0;
+        best.R = ((size_t)hi * k <= 24576) ? hi : hi / 2;
+        if ((size_t)best.R * k > 40960) best.threads = 0;
     }
     return best;
 }
@@ -396,11 +464,23 @@ bool pdl_enabled() {
     return v == 1;
 }
 
-int ctas_per_sm_wanted() {
+bool l2_prefetch_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("NNE_GEMV_L2PF");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+// Residency plan.  Default (1): one CTA per SM with a ring of about 100 KB, so that a CTA of the
+// NEXT kernel in the stream fits on the same SM and prefetches its weights while this one runs.
+// NNE_GEMV_CTAS=2: two CTAs of the same kernel per SM.  NNE_GEMV_CTAS=0: one CTA with a 200 KB ring.
+int residency_mode() {
     static int v = -1;
     if (v < 0) {
         const char *e = getenv("NNE_GEMV_CTAS");
-        v = (e && e[0] == '2') ? 2 : 1;
+        v = (e && e[0] == '2') ? 2 : (e && e[0] == '0') ? 0 : 1;
     }
     return v;
 }
@@ -410,9 +490,15 @@ int launch_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *
                const float *x, float *y, size_t n, size_t k, size_t ldy, int threads,
                cudaStream_t s) {
     const int stage_stride = (int)(((size_t)R * k + 127) & ~(size_t)127);
-    const int want = ctas_per_sm_wanted();
-    const size_t tail = sizeof(RingBars) + 2 * MAX_WARPS * R * MT * sizeof(float) + 128;
-    const size_t budget = (want == 2 ? 100 : 200) * 1024;
+    const int mode = residency_mode();
+    const int want = mode == 2 ? 2 : 1;
+    // rows per CTA (upper bound) -> shared scale/bias staging, unless that would eat the ring
+    const int grid_guess = ctx->sm_count * want;
+    int sb_rows = (int)((n + grid_guess - 1) / grid_guess) + 1;
+    if (sb_rows > 4 * threads) sb_rows = 0;  // the prologue stages at most 4 rows per thread
+    const size_t tail = sizeof(RingBars) + 2 * MAX_WARPS * R * MT * sizeof(float) +
+                        2 * (size_t)sb_rows * sizeof(float) + 128;
+    const size_t budget = (mode == 0 ? 200 : 100) * 1024;
     int stages = (int)((budget - tail) / (size_t)stage_stride);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
@@ -435,6 +521,7 @@ int launch_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *
     int grid = ctx->sm_count * occ;  // all CTAs resident at once: one wave, equal row ranges
     const int max_useful = (int)((n + R - 1) / R);
     if (grid > max_useful) grid = max_useful;
+    if (sb_rows && (int)((n + grid - 1) / grid) > sb_rows) sb_rows = 0;  // fewer CTAs than guessed
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
@@ -447,7 +534,8 @@ int launch_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_tma_kernel<MT, I, R>, q, scales, bias, x, y,
-                                       (int)n, (int)k, ldy, stages, stage_stride, ctx->err_word);
+                                       (int)n, (int)k, ldy, stages, stage_stride, sb_rows, l2_prefetch_enabled() ? 1 : 0,
+                                       ctx->err_word);
     count_launch();
     if (e != cudaSuccess)
         return fail(NNE_ERR_CUDA, "streaming kernel launch failed: %s", cudaGetErrorString(e));
@@ -455,6 +543,13 @@ int launch_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *
 }
 
 }  // namespace
+
+#ifdef NNE_TRACE
+extern "C" __attribute__((visibility("default"))) int nne_debug_read_trace(unsigned long long *out,
+                                                                           size_t n) {
+    return (int)cudaMemcpyFromSymbol(out, g_trace, n * sizeof(unsigned long long));
+}
+#endif
 
 // m is the number of activation rows of ONE launch (1..2).
 bool gemv_tma_supports(size_t n, size_t k, size_t m) {

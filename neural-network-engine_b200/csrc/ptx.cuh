@@ -24,6 +24,10 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrive without release ordering: does not wait for the thread's earlier loads to return.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint32_t bar) {
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar));
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
@@ -118,6 +122,44 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
+// L2 eviction policies: streamed-once data (weights) leaves first, small reused data (activations,
+// scales) stays.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ void bulk_load_1d_hint(uint32_t dst, const void *src, uint32_t bytes,
+                                                  uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+// Asks the memory system to bring [src, src+bytes) into L2 (no destination, no completion event).
+__device__ __forceinline__ void bulk_prefetch_l2(const void *src, uint32_t bytes, uint64_t policy) {
+    asm volatile("cp.async.bulk.prefetch.L2.global.L2::cache_hint [%0], %1, %2;" ::"l"(src),
+                 "r"(bytes), "l"(policy)
+                 : "memory");
+}
+__device__ __forceinline__ float4 ldg_f4_hint(const float4 *p, uint64_t policy) {
+    float4 v;
+    asm volatile("ld.global.nc.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p), "l"(policy));
+    return v;
+}
+__device__ __forceinline__ float ldg_f1_hint(const float *p, uint64_t policy) {
+    float v;
+    asm volatile("ld.global.nc.L2::cache_hint.f32 %0, [%1], %2;" : "=f"(v) : "l"(p), "l"(policy));
+    return v;
+}
+
 // Programmatic dependent launch: wait for the grids this one depends on / let dependents start.
 __device__ __forceinline__ void grid_dependency_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
