@@ -53,7 +53,7 @@ typedef enum nne_status {
 
 typedef struct nne_ctx nne_ctx;         /* one per device: streams, staging, SM count   */
 typedef struct nne_qlinear nne_qlinear; /* one device-resident int8 layer               */
-typedef struct nne_shard nne_shard;     /* one rank's column slice of a sharded layer   */
+typedef struct nne_plan nne_plan;       /* a fixed list of forwards run as one launch   */
 
 /* ---- status text -------------------------------------------------------------------------- */
 
@@ -144,6 +144,24 @@ NNE_API int nne_qlinear_forward_dev(nne_qlinear *ql, const float *x_dev, size_t 
  * write its slice straight into the gathered [m, N_total] layout. */
 NNE_API int nne_qlinear_forward_dev_strided(nne_qlinear *ql, const float *x_dev, size_t m,
                                             size_t k, float *y_dev, size_t ldy, void *stream);
+
+/* ---- plan: several independent forwards as one launch --------------------------------------
+ * A plan fixes a list of `count` forwards y_i[m, n_i] = QLinear_i.forward(x_i[m, k_i]) on device
+ * buffers that stay in place, and nne_qlinear_plan_run issues all of them on `stream`.  It takes
+ * the place of the back-to-back QLinear::forward calls a caller makes on projections that do
+ * not depend on each other - q/k/v (src/models/llama.rs:226-228), gate/up
+ * (src/models/llama.rs:344-346), or the per-layer timing loop of the decode benchmark - each
+ * of which is the contraction of src/nn/quantized.rs:164-193.  For m <= 2 and streaming-capable
+ * shapes the whole list is ONE kernel launch whose weight stream never drains between layers;
+ * otherwise the plan runs its layers one after the other.  Results are identical to `count`
+ * calls of nne_qlinear_forward_dev.  Layers must outlive the plan.                              */
+NNE_API int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *layers,
+                                    const float *const *x_dev, float *const *y_dev, size_t m,
+                                    nne_plan **out);
+NNE_API int nne_qlinear_plan_run(nne_plan *plan, void *stream);
+NNE_API int nne_qlinear_plan_destroy(nne_plan *plan);
+/* Number of kernel launches one run of the plan makes. */
+NNE_API int nne_qlinear_plan_launches(const nne_plan *plan);
 
 /* Which kernel a forward of m rows on this layer dispatches to: 1 = streaming GEMV (small m),
  * 2 = tcgen05/TMEM tensor-core kernel, 3 = generic kernel for shapes the others do not take. */

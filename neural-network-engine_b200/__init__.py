@@ -13,6 +13,7 @@ from .quantized import (  # noqa: F401
     InvalidArgument,
     Linear,
     QLinear,
+    QLinearPlan,
     ShapeMismatch,
     default_context,
 )

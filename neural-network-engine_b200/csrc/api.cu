@@ -5,7 +5,9 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <memory>
 #include <new>
+#include <vector>
 
 #include "common.cuh"
 
@@ -567,6 +569,91 @@ int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, siz
         cudaMemsetAsync(ctx->err_word, 0, sizeof(int), s);
         return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
     }
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+// ---- plan ---------------------------------------------------------------------------------------
+
+int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *layers,
+                            const float *const *x_dev, float *const *y_dev, size_t m,
+                            nne_plan **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    NNE_TRY(use_ctx(ctx));
+    if (count && (!layers || !x_dev || !y_dev))
+        return fail(NNE_ERR_INVALID_ARGUMENT, "null layer / x / y array");
+    if (count > 0x7fffffffu) return fail(NNE_ERR_INVALID_ARGUMENT, "too many layers");
+    std::unique_ptr<nne_plan> plan(new nne_plan());
+    plan->ctx = ctx;
+    plan->m = m;
+    bool fused = (m >= 1 && m <= 2);
+    for (size_t i = 0; i < count; ++i) {
+        nne_qlinear *ql = layers[i];
+        NNE_TRY(check_layer(ql));
+        if (ql->ctx != ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "layer %zu lives on another context", i);
+        if (m && ql->n && (!x_dev[i] || !y_dev[i]))
+            return fail(NNE_ERR_INVALID_ARGUMENT, "null x or y pointer for layer %zu", i);
+        plan->layers.push_back(ql);
+        plan->x.push_back(x_dev[i]);
+        plan->y.push_back(y_dev[i]);
+        StreamLayer L;
+        L.q = ql->q;
+        L.scales = ql->scales;
+        L.bias = ql->bias;
+        L.x = x_dev[i];
+        L.y = y_dev[i];
+        L.ldy = ql->n;
+        L.n = (int)ql->n;
+        L.k = (int)ql->k;
+        L.rw = stream_rows_per_stage(ql->k);
+        plan->descs.push_back(L);
+        fused = fused && aligned(ql->q, 16) && aligned(x_dev[i], 16) && aligned(y_dev[i], 4) &&
+                gemv_tma_supports(ql->n, ql->k, m);
+    }
+    plan->fused = fused && count > 0;
+    if (plan->fused && count > (size_t)STREAM_INLINE_LAYERS) {
+        NNE_CUDA_TRY(cudaMalloc(&plan->descs_dev, count * sizeof(StreamLayer)));
+        cudaError_t e = cudaMemcpy(plan->descs_dev, plan->descs.data(), count * sizeof(StreamLayer),
+                                   cudaMemcpyHostToDevice);
+        if (e != cudaSuccess) {
+            cudaFree(plan->descs_dev);
+            return fail(NNE_ERR_CUDA, "plan upload failed: %s", cudaGetErrorString(e));
+        }
+    }
+    *out = plan.release();
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_plan_run(nne_plan *plan, void *stream) {
+    NNE_GUARD_BEGIN
+    if (!plan || !plan->ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null plan");
+    if (plan->layers.empty() || plan->m == 0) return NNE_OK;
+    NNE_TRY(use_ctx(plan->ctx));
+    cudaStream_t s = (cudaStream_t)stream;
+    if (plan->fused)
+        return launch_stream_batch(plan->ctx, plan->descs.data(), plan->descs_dev,
+                                   (int)plan->descs.size(), plan->m, s);
+    for (size_t i = 0; i < plan->layers.size(); ++i)
+        NNE_TRY(forward_dev(plan->layers[i], plan->x[i], plan->m, plan->layers[i]->k, plan->y[i],
+                            plan->layers[i]->n, s));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_plan_launches(const nne_plan *plan) {
+    if (!plan) return 0;
+    return plan->fused ? 1 : (int)plan->layers.size();
+}
+
+int nne_qlinear_plan_destroy(nne_plan *plan) {
+    NNE_GUARD_BEGIN
+    if (!plan) return NNE_OK;
+    if (plan->ctx) cudaSetDevice(plan->ctx->device);
+    if (plan->descs_dev) cudaFree(plan->descs_dev);
+    delete plan;
     return NNE_OK;
     NNE_GUARD_END
 }

@@ -118,10 +118,30 @@ bool gemv_supports(size_t n, size_t k, size_t m);
 int launch_gemv(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                 const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                 cudaStream_t s);
-bool gemv_tma_supports(size_t n, size_t k, size_t m);  // m = rows of one launch, 1..4
+// One layer of a streaming launch (gemv_tma.cu).  x [m, k] and y [m, .] row stride ldy floats.
+struct StreamLayer {
+    const int8_t *q;
+    const float *scales;
+    const float *bias;  // or null
+    const float *x;
+    float *y;
+    size_t ldy;
+    int n, k;
+    int rw;  // weight rows per ring stage: stream_rows_per_stage(k)
+};
+constexpr int STREAM_INLINE_LAYERS = 8;  // descriptors passed in the kernel's parameter block
+struct StreamBatch {
+    int count;
+    const StreamLayer *dev;  // device copy of the descriptors when count > STREAM_INLINE_LAYERS
+    StreamLayer inl[STREAM_INLINE_LAYERS];
+};
+int stream_rows_per_stage(size_t k);
+bool gemv_tma_supports(size_t n, size_t k, size_t m);  // m = rows of one launch, 1..2
 int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                     const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                     cudaStream_t s);
+int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
+                        size_t m, cudaStream_t s);
 int launch_generic(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                    const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                    cudaStream_t s);
@@ -133,3 +153,16 @@ int launch_prefill(nne_qlinear *ql, const float *x, float *y, size_t m, size_t l
                    cudaStream_t s);
 
 }  // namespace nne
+
+#include <vector>
+
+struct nne_plan {
+    nne_ctx *ctx = nullptr;
+    size_t m = 0;
+    bool fused = false;  // the whole list runs as one streaming launch
+    std::vector<nne_qlinear *> layers;
+    std::vector<const float *> x;
+    std::vector<float *> y;
+    std::vector<nne::StreamLayer> descs;
+    nne::StreamLayer *descs_dev = nullptr;
+};

@@ -312,3 +312,46 @@ class QLinear:
             self.close()
         except Exception:
             pass
+
+
+class QLinearPlan:
+    """Several independent ``QLinear`` forwards on fixed device buffers, issued together.
+
+    Stands for the back-to-back ``forward`` calls a caller makes on projections that do not depend
+    on each other (q/k/v at src/models/llama.rs:226-228, gate/up at :344-346).  ``x_ptrs[i]`` is a
+    device pointer to ``[m, layers[i].in_features]`` f32, ``y_ptrs[i]`` to ``[m, out_features]``.
+    For m <= 2 the whole list is one kernel launch; results equal per-layer ``forward_device``."""
+
+    def __init__(self, layers, x_ptrs, y_ptrs, m: int, ctx: Optional[CudaContext] = None):
+        ctx = ctx or layers[0]._ctx or default_context()
+        n = len(layers)
+        hs = (C.c_void_p * n)(*[l._live_handle() for l in layers])
+        xs = (C.c_void_p * n)(*[int(p) for p in x_ptrs])
+        ys = (C.c_void_p * n)(*[int(p) for p in y_ptrs])
+        h = C.c_void_p()
+        try:
+            check(load().nne_qlinear_plan_create(ctx.handle, n, hs, xs, ys, m, C.byref(h)))
+        except NneError as e:
+            _raise_mapped(e)
+        self._h, self._layers, self._ctx = h, list(layers), ctx  # keep the layers alive
+
+    @property
+    def launches(self) -> int:
+        return int(load().nne_qlinear_plan_launches(self._h))
+
+    def run(self, stream: int = 0) -> None:
+        try:
+            check(load().nne_qlinear_plan_run(self._h, stream))
+        except NneError as e:
+            _raise_mapped(e)
+
+    def close(self):
+        if getattr(self, "_h", None) is not None:
+            load().nne_qlinear_plan_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass

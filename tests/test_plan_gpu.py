@@ -1,0 +1,70 @@
+"""A plan runs several independent forwards as one launch; its results must be bit-identical to
+the same forwards issued one by one (and therefore inherit their parity with the oracle)."""
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def build(nne, ctx, shapes, m, seed):
+    import torch
+    layers, xs, ys, refs = [], [], [], []
+    for i, (n, k, bias) in enumerate(shapes):
+        w = oracle.normal(seed, 10 * i, (n, k), 0.0, 0.02)
+        b = oracle.normal(seed, 10 * i + 1, (n,), 0.0, 0.1) if bias else None
+        ql = nne.QLinear.from_linear(nne.Linear(w, b), ctx)
+        x = oracle.normal(seed, 10 * i + 2, (m, k)) * np.float32(1.0 + i)
+        layers.append(ql)
+        xs.append(torch.from_numpy(x).cuda())
+        ys.append(torch.full((m, n), float("nan"), device="cuda"))
+        refs.append((ql, x, b))
+    return layers, xs, ys, refs
+
+
+@pytest.mark.parametrize("m", [1, 2])
+@pytest.mark.parametrize("shapes", [
+    [(300, 512, True), (129, 4096, False), (64, 11008, True)],
+    [(256, 1024, False)] * 3 + [(100, 2048, True)] * 4 + [(40, 4096, False)] * 5,  # > inline descriptors
+])
+def test_plan_equals_single_forwards(nne, ctx, shapes, m):
+    import torch
+    layers, xs, ys, refs = build(nne, ctx, shapes, m, 90 + m)
+    plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], m, ctx)
+    assert plan.launches == 1
+    s = torch.cuda.current_stream().cuda_stream
+    plan.run(s)
+    plan.run(s)  # twice: the second run must not depend on state left by the first
+    torch.cuda.synchronize()
+    ctx.check()
+    for (ql, x, b), y in zip(refs, ys):
+        single = ql.forward(x)
+        got = y.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), single.view(np.uint32))
+        qo, so = oracle.quantize_rows(ql.to_linear().weight / 1.0)  # codes round-trip exactly
+        tol, _ = oracle.tolerance(ql.qweight.reshape(ql.out_features, ql.in_features), ql.scales, x)
+        y_ref = oracle.forward(ql.qweight.reshape(ql.out_features, ql.in_features), ql.scales, b, x)
+        assert float((np.abs(got - y_ref) / tol).max()) <= 2e-2
+
+
+def test_plan_falls_back_for_other_shapes(nne, ctx):
+    import torch
+    # m = 3 and a k that is no multiple of 16: the plan runs its layers one after the other
+    shapes = [(64, 512, True), (33, 1001, False)]
+    layers, xs, ys, refs = build(nne, ctx, shapes, 3, 95)
+    plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], 3, ctx)
+    assert plan.launches == 2
+    plan.run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    for (ql, x, b), y in zip(refs, ys):
+        assert np.array_equal(y.cpu().numpy(), ql.forward(x))
+
+
+def test_plan_argument_errors(nne, ctx):
+    import torch
+    layers, xs, ys, _ = build(nne, ctx, [(64, 512, False)], 1, 96)
+    with pytest.raises(nne.InvalidArgument):
+        nne.QLinearPlan(layers, [0], [ys[0].data_ptr()], 1, ctx)
+    empty = nne.QLinearPlan(layers, [xs[0].data_ptr()], [ys[0].data_ptr()], 0, ctx)
+    empty.run(0)  # m = 0: nothing to do
