@@ -7,12 +7,15 @@ Workload (config.workload): the decode sweep on LLaMA-2-7B-shaped projections at
 QLinear K->N in {4096->4096, 4096->11008, 11008->4096}, weights ~ N(0, 0.02) quantized per
 output channel to int8, f32 activations ~ N(0, 1).  One step = one M=1 forward of every layer
 of a rotation set (several independently drawn copies of each shape, > L2 in total) so the
-weights come from HBM, not L2.  metric = int8-weight streaming rate in GB/s, counting the
-algorithmic bytes N*K + 4N + 4K + 4N per forward.  The same line carries the M=2048 prefill
-figure (TOPS) under "prefill".
+weights come from HBM, not L2.  The layers of a step do not depend on each other, so the step is
+issued as one plan (nne_qlinear_plan_run: one kernel launch that streams all the layers); the
+same step issued as one launch per layer is reported beside it under "per_layer_launches".
+metric = int8-weight streaming rate in GB/s, counting the algorithmic bytes
+N*K + 4N + 4K + 4N per forward.  The same line carries the M=2048 prefill figure (TFLOP/s) under
+"prefill".
 
 N > 1 (torchrun, one rank per GPU): every rank holds its own column shard of N-times-wider layers
-(weak scaling: per-GPU weight bytes fixed), computes its output slice and the slices are
+(weak scaling: per-GPU weight bytes fixed), computes its output slices and the step's slices are
 all-gathered over NCCL.
 
 --impl reference times the CPU restatement of the reference's Rayon/AVX2 path (oracle/) on the
@@ -36,6 +39,9 @@ SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008)]  # (N, K)
 REPLICAS = 4  # copies of each shape in the rotation set: 4 * 107 MB = 428 MB > 126 MB L2
 PREFILL_SHAPES = [(11008, 4096), (4096, 11008)]
 PREFILL_M = 2048
+# dram__bytes_read.sum + dram__bytes_write.sum of one qgemv_stream_kernel launch over the rotation
+# set, from the ncu capture summarised in profiles/; None until a capture exists.
+DRAM_TRAFFIC_PER_LAUNCH = None
 
 
 def algorithmic_bytes(n, k, m, bias=False):
@@ -68,7 +74,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100", "-i", str(self.gpu_index)],
+                 "-lms", "20", "-i", str(self.gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -220,28 +226,46 @@ def run_native(args):
         del w
         return h
 
-    # rotation set: REPLICAS independently drawn copies of each shape (this rank's shard when N>1)
-    layers = []
-    for rep in range(REPLICAS):
-        for si, (n, k) in enumerate(SHAPES):
-            h = make_layer(n, k, 2 + 1000 * rank + 10 * rep + si)
-            g = torch.Generator(device=dev)
-            g.manual_seed(100 + 10 * rep + si)  # activations are replicated: same on every rank
-            x = torch.randn(1, k, generator=g, device=dev, dtype=torch.float32)
-            y_full = torch.zeros(world, n, device=dev, dtype=torch.float32)  # gathered slices
-            layers.append({"h": h, "n": n, "k": k, "x": x, "y": y_full, "y_own": y_full[rank]})
+    # rotation set: REPLICAS independently drawn copies of each shape (this rank's shard when N>1).
+    # Outputs of all layers live in one slab per rank, so that N > 1 gathers a step's output
+    # slices with a single NCCL all-gather.
+    specs = [(n, k) for _ in range(REPLICAS) for (n, k) in SHAPES]
+    slab_len = sum(n for n, _ in specs)
+    gathered = torch.zeros(world, slab_len, device=dev, dtype=torch.float32)
+    own = gathered[rank]
+    layers, off = [], 0
+    for i, (n, k) in enumerate(specs):
+        h = make_layer(n, k, 2 + 1000 * rank + i)
+        g = torch.Generator(device=dev)
+        g.manual_seed(100 + i)  # activations are replicated: the same on every rank
+        x = torch.randn(1, k, generator=g, device=dev, dtype=torch.float32)
+        layers.append({"h": h, "n": n, "k": k, "x": x, "y_own": own[off:off + n]})
+        off += n
     step_bytes = sum(algorithmic_bytes(L["n"], L["k"], 1) for L in layers)
     stream = torch.cuda.current_stream()
 
+    # The step as ONE launch: a plan over the whole rotation set (nne_qlinear_plan_*).
+    nl = len(layers)
+    hs = (C.c_void_p * nl)(*[L["h"] for L in layers])
+    xs = (C.c_void_p * nl)(*[L["x"].data_ptr() for L in layers])
+    ys = (C.c_void_p * nl)(*[L["y_own"].data_ptr() for L in layers])
+    plan = C.c_void_p()
+    if lib.nne_qlinear_plan_create(ctx.handle, nl, hs, xs, ys, 1, C.byref(plan)) != 0:
+        raise RuntimeError(nne._lib.last_error())
+    launches_per_step = lib.nne_qlinear_plan_launches(plan)
+
     def step():
+        if lib.nne_qlinear_plan_run(plan, torch.cuda.current_stream().cuda_stream) != 0:
+            raise RuntimeError(nne._lib.last_error())
+        if world > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), own)
+
+    def per_layer_step():
         s = torch.cuda.current_stream().cuda_stream
         for L in layers:
-            st = lib.nne_qlinear_forward_dev(L["h"], L["x"].data_ptr(), 1, L["k"],
-                                             L["y_own"].data_ptr(), s)
-            if st != 0:
+            if lib.nne_qlinear_forward_dev(L["h"], L["x"].data_ptr(), 1, L["k"],
+                                           L["y_own"].data_ptr(), s) != 0:
                 raise RuntimeError(nne._lib.last_error())
-            if world > 1:
-                dist.all_gather_into_tensor(L["y"].view(-1), L["y_own"])
 
     def barrier():
         if world > 1:
@@ -251,21 +275,6 @@ def run_native(args):
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-
-    # One step is 12 launches of a few microseconds each: replaying it as a CUDA graph keeps the
-    # host's per-launch cost out of the device-timed region.  (N > 1 keeps eager launches: the
-    # NCCL all-gather between layers is issued by torch.distributed.)
-    graph = None
-    if world == 1 and not args.no_graph:
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
-        side.wait_stream(stream)
-        with torch.cuda.graph(graph, stream=side):
-            step()  # step() launches on torch's current stream, which is `side` here
-        torch.cuda.synchronize()
-        for _ in range(3):
-            graph.replay()
-        torch.cuda.synchronize()
 
     # device-timed region: K steps back to back on one stream
     sampler = ClockSampler(local_rank)
@@ -277,15 +286,10 @@ def run_native(args):
     barrier()
     e0.record(stream)
     for _ in range(args.steps):
-        if graph is not None:
-            graph.replay()
-        else:
-            step()
+        step()
     e1.record(stream)
     barrier()
     launches = lib.nne_launch_count() - launches0
-    if graph is not None:
-        launches = args.steps * len(layers)  # replayed kernel nodes, one per layer per step
     ms = e0.elapsed_time(e1)
     if world > 1:
         t = torch.tensor([ms], device=dev)
@@ -293,8 +297,35 @@ def run_native(args):
         ms = float(t.item())
     clocks = sampler.stop() if rank == 0 else None
     value = step_bytes * world * args.steps / (ms * 1e-3) / 1e9
-    per_launch_us = ms * 1e3 / (args.steps * len(layers))
+    per_launch_us = ms * 1e3 / (args.steps * launches_per_step)
     achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9  # one GPU's kernels
+
+    # The same step issued layer by layer (one launch per QLinear, replayed as a CUDA graph so the
+    # host's launch cost stays out): what a caller gets without a plan.
+    per_layer = None
+    if world == 1:
+        for _ in range(3):
+            per_layer_step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(stream)
+        with torch.cuda.graph(graph, stream=side):
+            per_layer_step()  # launches on torch's current stream, which is `side` here
+        torch.cuda.synchronize()
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        g1.record(stream)
+        torch.cuda.synchronize()
+        gms = g0.elapsed_time(g1)
+        per_layer = {"value": step_bytes * args.steps / (gms * 1e-3) / 1e9, "unit": "GB/s",
+                     "launches_per_step": nl, "avg_launch_us": gms * 1e3 / (args.steps * nl),
+                     "launch": "CUDA graph replay of 12 single-layer launches"}
 
     # end-to-end: the host-pointer entry point (what QLinear::forward calls), pinned host buffers,
     # H2D of x and D2H of y inside every call.
@@ -345,14 +376,16 @@ def run_native(args):
                        "m": 1, "replicas_per_shape": REPLICAS, "layers_per_step": len(layers),
                        "weight_bytes_per_step_per_gpu": sum(L["n"] * L["k"] for L in layers),
                        "l2": "rotation set of distinct weights larger than the 126 MB L2",
-                       "launch": "CUDA graph replay of one step" if graph is not None else "eager",
+                       "launch": "one plan launch per step (nne_qlinear_plan_run), steps back to back",
                        "parallelism": "1 GPU" if world == 1 else
-                       f"column shards over {world} GPUs + NCCL all-gather of output slices"},
+                       f"column shards over {world} GPUs + one NCCL all-gather of the step's output slices"},
             "roofline": {"bound": "hbm", "kernel": "qgemv_kernel", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "frac_of_nominal_8000": achieved / 8000.0,
-                         "avg_launch_us": per_launch_us, "traffic": None},
+                         "avg_launch_us": per_launch_us, "launches_per_step": launches_per_step,
+                         "algorithmic_bytes_per_launch": step_bytes / launches_per_step,
+                         "traffic": DRAM_TRAFFIC_PER_LAUNCH},
             "cpu_baseline": {"value": cpu_v, "unit": "GB/s", "cores": cpu_cores, "kind": "port",
                              "sample": cpu_sample},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
@@ -361,9 +394,12 @@ def run_native(args):
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if per_layer is not None:
+            out["per_layer_launches"] = per_layer
         if prefill is not None:
             out["prefill"] = prefill
         print(json.dumps(out))
+    lib.nne_qlinear_plan_destroy(plan)
     for L in layers:
         lib.nne_qlinear_destroy(L["h"])
     if world > 1:
@@ -422,10 +458,9 @@ def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
