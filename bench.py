@@ -40,8 +40,9 @@ REPLICAS = 4  # copies of each shape in the rotation set: 4 * 107 MB = 428 MB > 
 PREFILL_SHAPES = [(11008, 4096), (4096, 11008)]
 PREFILL_M = 2048
 # dram__bytes_read.sum + dram__bytes_write.sum of one qgemv_stream_kernel launch over the rotation
-# set, from the ncu capture summarised in profiles/; None until a capture exists.
-DRAM_TRAFFIC_PER_LAUNCH = None
+# set (read 428.5 MB + write 5.1 MB), from the ncu capture summarised in
+# profiles/qgemv_stream_kernel__decode_rotation_set.md.
+DRAM_TRAFFIC_PER_LAUNCH = 433.6e6
 
 
 def algorithmic_bytes(n, k, m, bias=False):
