@@ -145,6 +145,23 @@ NNE_API int nne_qlinear_forward_dev(nne_qlinear *ql, const float *x_dev, size_t 
 NNE_API int nne_qlinear_forward_dev_strided(nne_qlinear *ql, const float *x_dev, size_t m,
                                             size_t k, float *y_dev, size_t ldy, void *stream);
 
+/* Forward that never allocates.  It has no counterpart in the reference.  Meant for callers that
+ * may not allocate device memory while they run - a serving loop whose memory budget was handed
+ * out in full at start-up, or a thread that issues work while a collective is in flight and
+ * cannot risk the device-wide synchronisation an allocation can bring.  Same result as
+ * nne_qlinear_forward_dev for the shapes it takes: it always runs the tensor-core kernel, whose
+ * bf16 copy of the activations lives here in a fixed 8 MiB array in the library's device image
+ * (every GPU that loads the library holds it until the process exits) instead of a stream-ordered
+ * allocation.  Limits: in_features % 16 == 0, x_dev 16-byte aligned, and m * in_features <=
+ * 4 194 304 (4 Mi elements); anything larger is refused with NNE_ERR_INVALID_ARGUMENT and a
+ * message naming the limit.  The first call on a device looks the array's address up
+ * (cudaGetSymbolAddress); make that first call before any stream capture begins.  All calls on
+ * a device share the one array and it keeps the last call's contents, so two calls whose kernels
+ * can overlap on the GPU (different streams, no dependency) race: keep them on one stream or order
+ * them with events.  Calls no cudaMalloc/cudaFree or other allocating routine.                   */
+NNE_API int nne_qlinear_forward_dev_static(nne_qlinear *ql, const float *x_dev, size_t m, size_t k,
+                                           float *y_dev, void *stream);
+
 /* ---- plan: several independent forwards as one launch --------------------------------------
  * A plan fixes a list of `count` forwards y_i[m, n_i] = QLinear_i.forward(x_i[m, k_i]) on device
  * buffers that stay in place, and nne_qlinear_plan_run issues all of them on `stream`.  It takes

@@ -59,6 +59,8 @@ SIGNATURES = {
     "nne_qlinear_forward_dev_strided": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t,
                                                   C.c_size_t, C.c_void_p, C.c_size_t,
                                                   C.c_void_p]),
+    "nne_qlinear_forward_dev_static": (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t,
+                                                 C.c_void_p, C.c_void_p]),
     "nne_qlinear_plan_create": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp, c_void_pp, c_void_pp,
                                           C.c_size_t, c_void_pp]),
     "nne_qlinear_plan_run": (C.c_int, [C.c_void_p, C.c_void_p]),

@@ -426,3 +426,97 @@ int launch_prefill(nne_qlinear *ql, const float *x, float *y, size_t m, size_t l
 }
 
 }  // namespace nne
+
+// ---- forward without any allocation --------------------------------------------------------------
+// Some callers must not allocate device memory while they run: a serving loop that handed its whole
+// memory budget out at start-up, or a thread that issues work while a collective is in flight and
+// cannot afford the device-wide synchronisation an allocation may imply.  For them the bf16 copy of
+// the activations, which launch_prefill takes from a stream-ordered allocation, lives in this
+// fixed array instead.  Every GPU that loads the library holds these 8 MiB until the process exits.
+namespace nne {
+namespace {
+
+constexpr size_t STATIC_XBF16_ELEMS = (size_t)4 << 20;  // 4 Mi bf16 = 8 MiB: m * k may not exceed it
+static __device__ __align__(256) __nv_bfloat16 g_static_xbf16[STATIC_XBF16_ELEMS];
+
+// In host code `g_static_xbf16` is only a handle of the symbol, not a device address.  The address
+// is looked up once per device, with that device current, and cached here.
+std::mutex g_static_mu;
+__nv_bfloat16 *g_static_ptr[64] = {nullptr};
+
+int static_scratch_for(int device, __nv_bfloat16 **out) {
+    if (device < 0 || device >= 64) return fail(NNE_ERR_UNSUPPORTED, "device ordinal %d too large", device);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[device]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_xbf16);  // the caller made `device` current
+        if (e != cudaSuccess || !p) {
+            cudaGetLastError();
+            return fail(NNE_ERR_CUDA, "cudaGetSymbolAddress(g_static_xbf16) failed on device %d: %s",
+                        device, cudaGetErrorString(e));
+        }
+        g_static_ptr[device] = static_cast<__nv_bfloat16 *>(p);
+    }
+    *out = g_static_ptr[device];
+    return NNE_OK;
+}
+
+}  // namespace
+}  // namespace nne
+
+extern "C" int nne_qlinear_forward_dev_static(nne_qlinear *ql, const float *x_dev, size_t m, size_t k,
+                                              float *y_dev, void *stream) {
+    using namespace nne;
+    NNE_GUARD_BEGIN
+    if (!ql || !ql->ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null layer handle");
+    if (k != ql->k)
+        return fail(NNE_ERR_SHAPE_MISMATCH, "shape mismatch: expected [%zu], got [%zu]", ql->k, k);
+    if (m == 0 || ql->n == 0) return NNE_OK;
+    if (!x_dev || !y_dev) return fail(NNE_ERR_INVALID_ARGUMENT, "null activation or output pointer");
+    if (!ql->tmap_w || m > 0x7fffff00u || (reinterpret_cast<uintptr_t>(x_dev) & 15u) != 0)
+        return fail(NNE_ERR_UNSUPPORTED,
+                    "the allocation-free forward needs in_features %% 16 == 0 and 16-byte aligned x");
+    size_t elems;
+    if (__builtin_mul_overflow(m, k, &elems) || elems > STATIC_XBF16_ELEMS)
+        return fail(NNE_ERR_INVALID_ARGUMENT,
+                    "m * in_features = %zu * %zu exceeds the fixed workspace of %zu elements; use "
+                    "nne_qlinear_forward_dev or split the batch",
+                    m, k, STATIC_XBF16_ELEMS);
+    nne_ctx *ctx = ql->ctx;
+    NNE_TRY(use_ctx(ctx));
+    __nv_bfloat16 *xb = nullptr;
+    NNE_TRY(static_scratch_for(ctx->device, &xb));  // first call on a device: symbol look-up
+    cudaStream_t s = (cudaStream_t)stream;
+    static bool attr_set_static = false;
+    if (!attr_set_static) {
+        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set_static = true;
+    }
+    {
+        // The pre-pass overwrites [0, m*k) of the workspace; nothing in it has to start at zero
+        // and nothing beyond m*k is read (the tensor map below ends at row m).
+        const size_t n8 = elems / 8;
+        size_t blocks = (n8 + 255) / 256;
+        const size_t cap = (size_t)ctx->sm_count * 8;
+        if (blocks > cap) blocks = cap;
+        f32_to_bf16_kernel<<<(unsigned)blocks, 256, 0, s>>>(x_dev, xb, n8);
+        NNE_LAUNCH_CHECK();
+    }
+    CUtensorMap tmap_x;
+    NNE_TRY(make_map_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xb, ql->k, m, BK, BM,
+                        CU_TENSOR_MAP_SWIZZLE_128B));
+    const int tiles_m = (int)((m + BM - 1) / BM);
+    const int tiles_n = (int)((ql->n + BN - 1) / BN);
+    const long long tiles = (long long)tiles_m * tiles_n;
+    if (tiles > 0x7fffffff) return fail(NNE_ERR_UNSUPPORTED, "too many output tiles");
+    int grid = ctx->sm_count;
+    if (grid > tiles) grid = (int)tiles;
+    qlinear_prefill_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(
+        tmap_x, *static_cast<const CUtensorMap *>(ql->tmap_w), ql->scales, ql->bias, y_dev, (int)m,
+        (int)ql->n, (int)ql->k, ql->n, tiles_m, (int)tiles, ctx->err_word);
+    NNE_LAUNCH_CHECK();
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
