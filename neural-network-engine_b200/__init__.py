@@ -17,3 +17,4 @@ from .quantized import (  # noqa: F401
     ShapeMismatch,
     default_context,
 )
+from .sharding import ShardedQLinear, assemble, shard_rows, shard_sizes  # noqa: F401
