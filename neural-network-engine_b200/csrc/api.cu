@@ -635,7 +635,7 @@ int nne_qlinear_plan_run(nne_plan *plan, void *stream) {
     cudaStream_t s = (cudaStream_t)stream;
     if (plan->fused)
         return launch_stream_batch(plan->ctx, plan->descs.data(), plan->descs_dev,
-                                   (int)plan->descs.size(), plan->m, s);
+                                   (int)plan->descs.size(), plan->m, false, s);
     for (size_t i = 0; i < plan->layers.size(); ++i)
         NNE_TRY(forward_dev(plan->layers[i], plan->x[i], plan->m, plan->layers[i]->k, plan->y[i],
                             plan->layers[i]->n, s));

@@ -132,6 +132,7 @@ struct StreamLayer {
 constexpr int STREAM_INLINE_LAYERS = 8;  // descriptors passed in the kernel's parameter block
 struct StreamBatch {
     int count;
+    int reuse;  // the same weights appear again later in the list: do not mark them evict-first
     const StreamLayer *dev;  // device copy of the descriptors when count > STREAM_INLINE_LAYERS
     StreamLayer inl[STREAM_INLINE_LAYERS];
 };
@@ -140,8 +141,11 @@ bool gemv_tma_supports(size_t n, size_t k, size_t m);  // m = rows of one launch
 int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                     const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                     cudaStream_t s);
+int launch_gemv_tma_passes(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
+                           const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
+                           cudaStream_t s);
 int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
-                        size_t m, cudaStream_t s);
+                        size_t m, bool reuse, cudaStream_t s);
 int launch_generic(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                    const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                    cudaStream_t s);

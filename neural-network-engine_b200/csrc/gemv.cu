@@ -303,6 +303,8 @@ int launch_gemv(nne_ctx *ctx, const int8_t *q, const float *scales, const float 
         const char *e = getenv("NNE_NO_TMA_GEMV");
         return e && e[0] == '1';
     }();
+    if (!no_tma && m > 2 && m <= 2 * (size_t)STREAM_INLINE_LAYERS && gemv_tma_supports(n, k, 2))
+        return launch_gemv_tma_passes(ctx, q, scales, bias, x, y, n, k, m, ldy, s);
     size_t r = 0;
     while (r < m) {
         const size_t left = m - r;

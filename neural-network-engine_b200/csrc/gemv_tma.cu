@@ -263,7 +263,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
     if (warp == MATH_WARPS + PREP_WARPS) {
         // ---------------- producer: weights only, may run ahead of the previous kernel ----------
         if (lane == 0) {
-            const uint64_t pol_stream = l2_policy_evict_first();
+            const uint64_t pol_stream = batch.reuse ? l2_policy_evict_normal() : l2_policy_evict_first();
             int slot = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -524,12 +524,13 @@ bool gemv_tma_supports(size_t n, size_t k, size_t m) {
 // Launches the streaming kernel over `count` layers (descriptors in host memory `host`; for more
 // than STREAM_INLINE_LAYERS layers `dev` must hold the same descriptors in device memory).
 int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
-                        size_t m, cudaStream_t s) {
+                        size_t m, bool reuse, cudaStream_t s) {
     if (count <= 0) return NNE_OK;
     if (count > STREAM_INLINE_LAYERS && !dev)
         return fail(NNE_ERR_INVALID_ARGUMENT, "a batch of %d layers needs device descriptors", count);
     StreamBatch batch;
     batch.count = count;
+    batch.reuse = reuse ? 1 : 0;
     batch.dev = count > STREAM_INLINE_LAYERS ? dev : nullptr;
     size_t kmax = 0, slot_payload = 0, nmax = 0, nmin = (size_t)-1;
     for (int i = 0; i < count; ++i) {
@@ -579,7 +580,34 @@ int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const fl
     L.n = (int)n;
     L.k = (int)k;
     L.rw = stream_rows_per_stage(k);
-    return launch_stream_batch(ctx, &L, nullptr, 1, m, s);
+    return launch_stream_batch(ctx, &L, nullptr, 1, m, false, s);
+}
+
+// m > 2 activation rows on one layer: passes of two rows, all in ONE launch.  The first pass
+// brings the weights from HBM, the later ones find them in L2 (a 7B-shaped layer is 17-45 MB of
+// the 126 MB L2), and no launch gap separates the passes.
+int launch_gemv_tma_passes(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
+                           const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
+                           cudaStream_t s) {
+    const size_t pairs = m / 2;
+    if (pairs > (size_t)STREAM_INLINE_LAYERS)
+        return fail(NNE_ERR_UNSUPPORTED, "m=%zu needs more passes than one launch holds", m);
+    StreamLayer L[STREAM_INLINE_LAYERS];
+    for (size_t p = 0; p < pairs; ++p) {
+        L[p].q = q;
+        L[p].scales = scales;
+        L[p].bias = bias;
+        L[p].x = x + 2 * p * k;
+        L[p].y = y + 2 * p * ldy;
+        L[p].ldy = ldy;
+        L[p].n = (int)n;
+        L[p].k = (int)k;
+        L[p].rw = stream_rows_per_stage(k);
+    }
+    if (pairs) NNE_TRY(launch_stream_batch(ctx, L, nullptr, (int)pairs, 2, pairs > 1 || (m & 1), s));
+    if (m & 1)
+        NNE_TRY(launch_gemv_tma(ctx, q, scales, bias, x + (m - 1) * k, y + (m - 1) * ldy, n, k, 1, ldy, s));
+    return NNE_OK;
 }
 
 }  // namespace nne

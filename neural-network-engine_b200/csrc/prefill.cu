@@ -5,10 +5,10 @@
 // far inside the path's tolerance (1e-3 of the a-priori bound per output channel).
 //
 // One persistent CTA per SM walks 128 x 256 output tiles.  Per 64-wide k-block and stage:
-//   warp 0      TMA producer: bf16 activations tile [128 x 64] (128B-swizzled, straight into
-//               the UMMA layout) and int8 weight tile [256 x 64] (dense staging buffer)
-//   warps 2-9   dequantizers: int8 staging -> bf16 in the 128B-swizzled K-major UMMA layout,
-//               then fence.proxy.async and an mbarrier arrive
+//   warp 0      TMA producer, 4 stages deep: bf16 activations tile [128 x 64] (128B-swizzled,
+//               straight into the UMMA layout) and int8 weight tile [256 x 64] (dense staging)
+//   warps 2-9   dequantizers: int8 staging -> one of two bf16 tiles in the 128B-swizzled K-major
+//               UMMA layout, then fence.proxy.async and an mbarrier arrive
 //   warp 1      one thread issues 4 tcgen05.mma (128x256x16, kind::f16, bf16 in, f32 out in TMEM)
 //               and tcgen05.commit releases the stage
 //   warps 10-13 epilogue: tcgen05.ld of the finished accumulator (double buffered, 2 x 256 TMEM
@@ -27,13 +27,16 @@
 namespace nne {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 3;
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int STAGES = 4;    // TMA ring: bf16 activations tile + int8 weights tile per stage
+constexpr int BSTAGES = 2;   // ring of dequantized bf16 weight tiles (dequantizers -> MMA)
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB bf16 activations
 constexpr int B_BYTES = BN * BK * 2;   // 32 KB bf16 weights (dequantized here)
 constexpr int WQ_BYTES = BN * BK;      // 16 KB int8 weights (TMA staging)
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + WQ_BYTES;
+constexpr int STAGE_BYTES = A_BYTES + WQ_BYTES;  // one TMA stage
 constexpr int BAR_BYTES = 256;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // + 1 KB alignment slack
+// TMA stages first, then the bf16 weight tiles (all 1 KB aligned), + 1 KB alignment slack
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BSTAGES * B_BYTES + BAR_BYTES + 1024;
 constexpr int NUM_CONVERT_WARPS = 8, NUM_EPI_WARPS = 4;
 constexpr int THREADS = 32 * (2 + NUM_CONVERT_WARPS + NUM_EPI_WARPS);  // 448
 constexpr uint32_t TMEM_COLS = 512;
@@ -72,8 +75,9 @@ __device__ __forceinline__ void cvt_i8x4_bf16(uint32_t w, uint32_t &lo, uint32_t
 
 struct Bars {
     uint64_t full[STAGES];     // TMA bytes of the stage have landed
-    uint64_t bready[STAGES];   // bf16 weights of the stage are written and fenced
-    uint64_t empty[STAGES];    // the stage's MMAs have completed
+    uint64_t empty[STAGES];    // the MMAs that read the stage's activations have completed
+    uint64_t bready[BSTAGES];  // bf16 weight tile is written and fenced
+    uint64_t bfree[BSTAGES];   // the MMAs that read the bf16 weight tile have completed
     uint64_t acc_full[2];      // accumulator buffer holds a finished tile
     uint64_t acc_empty[2];     // accumulator buffer has been drained
     uint32_t tmem_base;
@@ -90,7 +94,8 @@ qlinear_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    Bars *bars = reinterpret_cast<Bars *>(smem + STAGES * STAGE_BYTES);
+    uint8_t *btiles = smem + STAGES * STAGE_BYTES;
+    Bars *bars = reinterpret_cast<Bars *>(btiles + BSTAGES * B_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (k + BK - 1) / BK;
     volatile int *abort_flag = &bars->abort_flag;
@@ -98,8 +103,11 @@ qlinear_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
-            mbar_init(smem_u32(&bars->bready[s]), NUM_CONVERT_WARPS);
             mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int b = 0; b < BSTAGES; ++b) {
+            mbar_init(smem_u32(&bars->bready[b]), NUM_CONVERT_WARPS);
+            mbar_init(smem_u32(&bars->bfree[b]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars->acc_full[b]), 1);
@@ -135,7 +143,7 @@ qlinear_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                     const uint32_t full = smem_u32(&bars->full[stage]);
                     mbar_arrive_expect_tx(full, A_BYTES + WQ_BYTES);
                     tma_load_2d(smem_u32(st), &tmap_x, kb * BK, m0, full);
-                    tma_load_2d(smem_u32(st + A_BYTES + B_BYTES), &tmap_w, kb * BK, n0, full);
+                    tma_load_2d(smem_u32(st + A_BYTES), &tmap_w, kb * BK, n0, full);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -153,8 +161,8 @@ qlinear_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            int stage = 0, acc = 0;
-            uint32_t phase = 0, acc_phase = 0;
+            int stage = 0, acc = 0, bst = 0;
+            uint32_t phase = 0, acc_phase = 0, bphase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 ok = mbar_wait(smem_u32(&bars->acc_empty[acc]), acc_phase ^ 1, abort_flag, err, 2);
@@ -163,20 +171,21 @@ qlinear_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
                 const uint32_t d_tmem = tmem_base + (uint32_t)acc * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 3) &&
-                         mbar_wait(smem_u32(&bars->bready[stage]), phase, abort_flag, err, 4);
+                         mbar_wait(smem_u32(&bars->bready[bst]), bphase, abort_flag, err, 4);
                     if (!ok) break;
                     tc_fence_after();
-                    uint8_t *st = smem + stage * STAGE_BYTES;
-                    const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(st));
-                    const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(st + A_BYTES));
+                    const uint64_t a_desc = make_kmajor_sw128_desc(smem_u32(smem + stage * STAGE_BYTES));
+                    const uint64_t b_desc = make_kmajor_sw128_desc(smem_u32(btiles + bst * B_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < BK / 16; ++kk) {
                         // +32 bytes per 16-element k step inside the 128-byte swizzle span
                         umma_bf16(d_tmem, a_desc + (uint64_t)(kk * 2), b_desc + (uint64_t)(kk * 2),
                                   IDESC, (kb | kk) != 0 ? 1u : 0u);
                     }
-                    umma_commit(smem_u32(&bars->empty[stage]));
+                    umma_commit(smem_u32(&bars->empty[stage]));  // activations + int8 staging reusable
+                    umma_commit(smem_u32(&bars->bfree[bst]));    // bf16 weight tile reusable
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++bst == BSTAGES) { bst = 0; bphase ^= 1; }
                 }
                 if (!ok) break;
                 umma_commit(smem_u32(&bars->acc_full[acc]));
@@ -187,34 +196,39 @@ qlinear_prefill_kernel(const __grid_constant__ CUtensorMap tmap_x,
         // ---------------- dequantizers: int8 staging -> swizzled bf16 ----------------
         const int ct = threadIdx.x - 64;          // 0..255
         const int chunk = ct & 3;                 // 16-byte chunk (16 k values) of the 64-byte row
-        int stage = 0;
-        uint32_t phase = 0;
+        const int row0 = ct >> 2, sw = row0 & 7;  // row & 7 is the same for the thread's four rows
+        const int off0 = ((2 * chunk) ^ sw) << 4, off1 = ((2 * chunk + 1) ^ sw) << 4;
+        int stage = 0, bst = 0;
+        uint32_t phase = 0, bphase = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             for (int kb = 0; kb < num_kb; ++kb) {
-                ok = mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 5);
+                ok = mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 5) &&
+                     mbar_wait(smem_u32(&bars->bfree[bst]), bphase ^ 1, abort_flag, err, 7);
                 if (!ok) break;
-                uint8_t *st = smem + stage * STAGE_BYTES;
-                const uint8_t *wq = st + A_BYTES + B_BYTES;
-                uint8_t *bt = st + A_BYTES;
+                // all four loads first (the stores below could alias them for the compiler), then
+                // convert and store
+                const uint4 *wq4 = reinterpret_cast<const uint4 *>(smem + stage * STAGE_BYTES + A_BYTES) + ct;
+                uint4 v[BN / 64];
+#pragma unroll
+                for (int it = 0; it < BN / 64; ++it) v[it] = wq4[it * 256];
+                uint8_t *rowp0 = btiles + bst * B_BYTES + (row0 >> 3) * 1024 + sw * 128;
 #pragma unroll
                 for (int it = 0; it < BN / 64; ++it) {
-                    const int row = (ct >> 2) + it * 64;
-                    const uint4 v = *reinterpret_cast<const uint4 *>(wq + row * BK + chunk * 16);
                     uint4 o0, o1;
-                    cvt_i8x4_bf16(v.x, o0.x, o0.y);
-                    cvt_i8x4_bf16(v.y, o0.z, o0.w);
-                    cvt_i8x4_bf16(v.z, o1.x, o1.y);
-                    cvt_i8x4_bf16(v.w, o1.z, o1.w);
-                    uint8_t *rowp = bt + (row >> 3) * 1024 + (row & 7) * 128;
-                    const int sw = row & 7;
-                    *reinterpret_cast<uint4 *>(rowp + (((2 * chunk) ^ sw) << 4)) = o0;
-                    *reinterpret_cast<uint4 *>(rowp + (((2 * chunk + 1) ^ sw) << 4)) = o1;
+                    cvt_i8x4_bf16(v[it].x, o0.x, o0.y);
+                    cvt_i8x4_bf16(v[it].y, o0.z, o0.w);
+                    cvt_i8x4_bf16(v[it].z, o1.x, o1.y);
+                    cvt_i8x4_bf16(v[it].w, o1.z, o1.w);
+                    uint8_t *rowp = rowp0 + it * 8 * 1024;  // 64 rows further = 8 groups of 8 rows
+                    *reinterpret_cast<uint4 *>(rowp + off0) = o0;
+                    *reinterpret_cast<uint4 *>(rowp + off1) = o1;
                 }
                 fence_proxy_async();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->bready[stage]));
+                if (lane == 0) mbar_arrive(smem_u32(&bars->bready[bst]));
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                if (++bst == BSTAGES) { bst = 0; bphase ^= 1; }
             }
         }
     } else {
