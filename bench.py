@@ -380,7 +380,7 @@ def run_native(args):
                        "launch": "one plan launch per step (nne_qlinear_plan_run), steps back to back",
                        "parallelism": "1 GPU" if world == 1 else
                        f"column shards over {world} GPUs + one NCCL all-gather of the step's output slices"},
-            "roofline": {"bound": "hbm", "kernel": "qgemv_kernel", "achieved": achieved,
+            "roofline": {"bound": "hbm", "kernel": "qgemv_stream_kernel", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "frac_of_nominal_8000": achieved / 8000.0,
@@ -446,13 +446,15 @@ def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):
         lib.nne_qlinear_destroy(h)
         del x, y
     tf = tot_flops / (tot_ms * 1e-3) / 1e12
-    res["roofline"] = {"bound": "tensor", "kernel": "qlinear_prefill_kernel", "achieved": tf,
+    res["roofline"] = {"bound": "tensor", "kernel": "qlinear_prefill_i8_kernel", "achieved": tf,
                        "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                        "frac": tf / peaks["bf16_tflops"], "peak_source": peaks["source"],
                        "frac_of_nominal_2250": tf / 2250.0}
     res["value"] = tf
     res["unit"] = "TFLOP/s"
-    res["dtype"] = "bf16 x bf16 -> f32 (int8 weights dequantized to bf16 in shared memory)"
+    res["dtype"] = "s8 x s8 -> s32 (tcgen05 kind::i8; x as two int8 digit planes), f32 epilogue"
+    res["roofline"]["note"] = ("peak = measured cuBLAS bf16 GEMM; two int8 digit MMAs at twice the "
+                               "bf16 rate cost what one bf16 MMA would")
     return res
 
 

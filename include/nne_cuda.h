@@ -148,9 +148,10 @@ NNE_API int nne_qlinear_forward_dev_strided(nne_qlinear *ql, const float *x_dev,
 /* Forward that never allocates.  It has no counterpart in the reference.  Meant for callers that
  * may not allocate device memory while they run - a serving loop whose memory budget was handed
  * out in full at start-up, or a thread that issues work while a collective is in flight and
- * cannot risk the device-wide synchronisation an allocation can bring.  Same result as
- * nne_qlinear_forward_dev for the shapes it takes: it always runs the tensor-core kernel, whose
- * bf16 copy of the activations lives here in a fixed 8 MiB array in the library's device image
+ * cannot risk the device-wide synchronisation an allocation can bring.  Same contraction as
+ * nne_qlinear_forward_dev, within the same tolerance: it always runs the bf16 tensor-core kernel
+ * (codes dequantized to bf16 in shared memory, activations rounded to bf16), whose bf16 copy of
+ * the activations lives here in a fixed 8 MiB array in the library's device image
  * (every GPU that loads the library holds it until the process exits) instead of a stream-ordered
  * allocation.  Limits: in_features % 16 == 0, x_dev 16-byte aligned, and m * in_features <=
  * 4 194 304 (4 Mi elements); anything larger is refused with NNE_ERR_INVALID_ARGUMENT and a
@@ -181,7 +182,8 @@ NNE_API int nne_qlinear_plan_destroy(nne_plan *plan);
 NNE_API int nne_qlinear_plan_launches(const nne_plan *plan);
 
 /* Which kernel a forward of m rows on this layer dispatches to: 1 = streaming GEMV (small m),
- * 2 = tcgen05/TMEM tensor-core kernel, 3 = generic kernel for shapes the others do not take. */
+ * 2 = tcgen05/TMEM tensor-core kernel (integer form; NNE_PREFILL=bf16 in the environment selects
+ * the bf16 form), 3 = generic kernel for shapes the others do not take. */
 NNE_API int nne_qlinear_kernel_for(const nne_qlinear *ql, size_t m);
 /* Number of kernels this library has launched in the calling process (all contexts). */
 NNE_API uint64_t nne_launch_count(void);

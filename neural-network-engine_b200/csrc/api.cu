@@ -3,6 +3,7 @@
 // lives in quantize.cu, gemv.cu and prefill.cu.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <memory>
@@ -85,11 +86,21 @@ int alloc_layer(nne_ctx *ctx, size_t n, size_t k, bool has_bias, nne_qlinear **o
     return NNE_OK;
 }
 
+// NNE_PREFILL=bf16 selects the bf16 tensor-core kernel (int8 codes dequantized in shared memory)
+// instead of the integer one.
+bool prefill_bf16_forced() {
+    static const bool v = [] {
+        const char *e = getenv("NNE_PREFILL");
+        return e && e[0] == 'b';
+    }();
+    return v;
+}
+
 // Kernel choice for a forward of m rows.  1 = streaming GEMV, 2 = tensor-core, 3 = generic.
 int pick_kernel(const nne_qlinear *ql, size_t m, const float *x, const float *y) {
     const bool base_ok = aligned(ql->q, 16) && (x == nullptr || aligned(x, 16)) &&
                          (y == nullptr || aligned(y, 4));
-    if (m > 16 && base_ok && prefill_supports(ql, m)) return 2;
+    if (m > 16 && base_ok && (prefill_i8_supports(ql, m) || prefill_supports(ql, m))) return 2;
     if (base_ok && gemv_supports(ql->n, ql->k, m)) return 1;
     return 3;
 }
@@ -111,7 +122,9 @@ int forward_dev(nne_qlinear *ql, const float *x, size_t m, size_t k, float *y, s
         return launch_generic(ql->ctx, ql->q, ql->scales, ql->bias, x, y, ql->n, 0, m, ldy, s);
     }
     switch (pick_kernel(ql, m, x, y)) {
-        case 2: return launch_prefill(ql, x, y, m, ldy, s);
+        case 2:
+            if (prefill_i8_supports(ql, m) && !prefill_bf16_forced()) return launch_prefill_i8(ql, x, y, m, ldy, s);
+            return launch_prefill(ql, x, y, m, ldy, s);
         case 1:
             return launch_gemv(ql->ctx, ql->q, ql->scales, ql->bias, x, y, ql->n, ql->k, m, ldy, s);
         default:
@@ -388,6 +401,7 @@ int nne_qlinear_create_from_f32_dev(nne_ctx *ctx, const float *w_dev, const floa
         if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "quantize failed: %s", cudaGetErrorString(e));
     }
     if (st == NNE_OK) st = prefill_prepare_layer(ql);
+    if (st == NNE_OK) st = prefill_i8_prepare_layer(ql);
     if (st != NNE_OK) {
         nne_qlinear_destroy(ql);
         return st;
@@ -427,6 +441,7 @@ int nne_qlinear_create_from_f32(nne_ctx *ctx, const float *w_host, const float *
             st = fail(NNE_ERR_CUDA, "layer upload failed: %s", cudaGetErrorString(e));
     }
     if (st == NNE_OK) st = prefill_prepare_layer(ql);
+    if (st == NNE_OK) st = prefill_i8_prepare_layer(ql);
     if (st != NNE_OK) {
         nne_qlinear_destroy(ql);
         return st;
@@ -464,6 +479,7 @@ int nne_qlinear_create_from_i8(nne_ctx *ctx, const int8_t *q_host, const float *
     int st = NNE_OK;
     if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "layer upload failed: %s", cudaGetErrorString(e));
     if (st == NNE_OK) st = prefill_prepare_layer(ql);
+    if (st == NNE_OK) st = prefill_i8_prepare_layer(ql);
     if (st != NNE_OK) {
         nne_qlinear_destroy(ql);
         return st;
@@ -478,6 +494,7 @@ int nne_qlinear_destroy(nne_qlinear *ql) {
     if (!ql) return NNE_OK;
     cudaSetDevice(ql->device);
     prefill_release_layer(ql);
+    prefill_i8_release_layer(ql);
     if (ql->own) {
         if (ql->q) cudaFree(ql->q);
         if (ql->scales) cudaFree(ql->scales);

@@ -94,7 +94,8 @@ struct nne_qlinear {
     float *scales = nullptr;  // [n]
     float *bias = nullptr;    // [n] or null
     bool own = true;
-    void *tmap_w = nullptr;   // host copy of the TMA descriptor of q (tensor path), or null
+    void *tmap_w = nullptr;   // host copy of the TMA descriptor of q (bf16 tensor path), or null
+    void *tmap_w8 = nullptr;  // host copy of the swizzled TMA descriptor of q (int8 tensor path)
 };
 
 namespace nne {
@@ -155,6 +156,11 @@ int prefill_prepare_layer(nne_qlinear *ql);  // builds the weight TMA descriptor
 void prefill_release_layer(nne_qlinear *ql);
 int launch_prefill(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
                    cudaStream_t s);
+bool prefill_i8_supports(const nne_qlinear *ql, size_t m);
+int prefill_i8_prepare_layer(nne_qlinear *ql);
+void prefill_i8_release_layer(nne_qlinear *ql);
+int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
+                      cudaStream_t s);
 
 }  // namespace nne
 

@@ -361,6 +361,12 @@ int make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, size_t elem_bytes, con
 
 }  // namespace
 
+int tma_make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, size_t elem_bytes, const void *base,
+                    size_t inner, size_t outer, uint32_t box_inner, uint32_t box_outer,
+                    CUtensorMapSwizzle sw) {
+    return make_map_2d(map, dt, elem_bytes, base, inner, outer, box_inner, box_outer, sw);
+}
+
 bool prefill_supports(const nne_qlinear *ql, size_t m) {
     if (!ql || !ql->tmap_w) return false;
     if (m == 0 || m > 0x7fffff00u) return false;

@@ -1,0 +1,394 @@
+// Prefill-shape forward (m > 16) on the 5th-generation tensor cores, integer form:
+//   y[r,j] = (sum_i x[r,i] * q[j,i]) * scales[j] (+ bias[j])
+// (device form of QLinear::forward_quantized, reference src/nn/quantized.rs:164-193, for large m).
+//
+// The int8 codes are fed to tcgen05.mma.kind::i8 exactly as they lie in memory - no dequantizer,
+// no extra pass over shared memory.  Each activation row is put on a power-of-two fixed-point
+// grid, v = rint(x * 2^e) with |v| <= 2^13 (e from the row's largest |x|), and split into two
+// balanced base-128 digits d0, d1 held as int8 (a small pre-pass).  Two MMAs per k-step accumulate
+// D0 = X0.W^T and D1 = X1.W^T as EXACT int32 sums in two TMEM accumulators, and the epilogue forms
+// dot = (D0 + 128*D1) * 2^-e, then * scales[j] and + bias[j] as separate fp32 operations like the
+// reference (:187-190).  The one approximation is the rounding of x to the grid: at most
+// 2^-14 * 2^ceil(log2 max|x_r|) per element, i.e. a result error below 6.2e-5 of the a-priori
+// bound ||x||inf * scale_j * sum|q_jk| the tolerance is written against (tolerance: 1e-3 of it) -
+// 32 times tighter than rounding x to bf16 could guarantee.  The int8 pipe runs at twice the bf16
+// rate, so two digit MMAs cost what one bf16 MMA would.  A row of x holding Inf or NaN yields NaN
+// for that row.
+//
+// One persistent CTA per SM walks 128 x 256 output tiles.  Per 128-wide k-block and stage:
+//   warp 0      TMA producer: int8 weight tile [256 x 128] and the two activation digit tiles
+//               [128 x 128], all 128B-swizzled straight into the UMMA K-major layout; no multicast
+//   warp 1      one thread issues 2 x 4 tcgen05.mma (128x256x32, kind::i8) and tcgen05.commit
+//   warps 2-5   epilogue: tcgen05.ld of both accumulators, combine, scale, bias, f32 store
+// Every mbarrier wait is bounded (~2 s): on expiry the context's device error word is set and the
+// CTA drains, frees its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace nne {
+namespace {
+
+constexpr int BM = 128, BN = 256, BKB = 128;  // BKB: bytes (= int8 elements) of K per k-block
+constexpr int STAGES = 3;
+constexpr int W_BYTES = BN * BKB;   // 32 KB
+constexpr int X_BYTES = BM * BKB;   // 16 KB per digit
+constexpr int STAGE_BYTES = W_BYTES + 2 * X_BYTES;  // 64 KB
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
+constexpr int NUM_EPI_WARPS = 4;
+constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
+constexpr uint32_t TMEM_COLS = 512;  // two int32 accumulators of 256 columns
+
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);   // start address
+    d |= (uint64_t)1 << 16;                       // leading byte offset (ignored when swizzled)
+    d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset: 8 rows * 128 B
+    d |= (uint64_t)1 << 46;                       // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D = s32, A = B = signed int8, both K-major, M = 128, N = 256.
+constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                              ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(IDESC_I8), "r"(accumulate)
+        : "memory");
+}
+
+// D0 + 128*D1 as one correctly rounded float (the int64 sum is exact).
+__device__ __forceinline__ float combine(uint32_t d0, uint32_t d1) {
+    return __ll2float_rn((long long)(int)d0 + ((long long)(int)d1 << 7));
+}
+
+struct Bars {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t acc_full;
+    uint64_t acc_empty;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(Bars) <= BAR_BYTES, "barrier block too large");
+
+__global__ void __launch_bounds__(THREADS, 1)
+qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                          const __grid_constant__ CUtensorMap tmap_x0,
+                          const __grid_constant__ CUtensorMap tmap_x1,
+                          const float *__restrict__ unscale, const float *__restrict__ scales,
+                          const float *__restrict__ bias, float *__restrict__ y, int m, int n, int k,
+                          size_t ldy, int tiles_m, int num_tiles, int *err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    Bars *bars = reinterpret_cast<Bars *>(smem + STAGES * STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (k + BKB - 1) / BKB;
+    volatile int *abort_flag = &bars->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bars->acc_full), 1);
+        mbar_init(smem_u32(&bars->acc_empty), NUM_EPI_WARPS);
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&bars->tmem_base)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, err, 0x21);
+                    if (!ok) break;
+                    uint8_t *st = smem + stage * STAGE_BYTES;
+                    const uint32_t full = smem_u32(&bars->full[stage]);
+                    mbar_arrive_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(smem_u32(st), &tmap_w, kb * BKB, n0, full);
+                    tma_load_2d(smem_u32(st + W_BYTES), &tmap_x0, kb * BKB, m0, full);
+                    tma_load_2d(smem_u32(st + W_BYTES + X_BYTES), &tmap_x1, kb * BKB, m0, full);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // Gave up: let copies that are still in flight land before the CTA exits.
+                for (int s = 0; s < STAGES; ++s) {
+                    const unsigned long long t0 = globaltimer_ns();
+                    while (!mbar_try_wait(smem_u32(&bars->full[s]), 0) &&
+                           !mbar_try_wait(smem_u32(&bars->full[s]), 1) &&
+                           globaltimer_ns() - t0 < 100000000ull) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                // the epilogue has drained both accumulators of the previous tile
+                ok = mbar_wait(smem_u32(&bars->acc_empty), acc_phase ^ 1, abort_flag, err, 0x22);
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 0x23);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint8_t *st = smem + stage * STAGE_BYTES;
+                    const uint64_t w_desc = make_kmajor_sw128_desc(smem_u32(st));
+                    const uint64_t x0_desc = make_kmajor_sw128_desc(smem_u32(st + W_BYTES));
+                    const uint64_t x1_desc = make_kmajor_sw128_desc(smem_u32(st + W_BYTES + X_BYTES));
+#pragma unroll
+                    for (int kk = 0; kk < BKB / 32; ++kk) {
+                        // +32 bytes per 32-element k step inside the 128-byte swizzle span
+                        const uint32_t accum = (kb | kk) != 0 ? 1u : 0u;
+                        umma_i8(tmem_base, x0_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), accum);
+                        umma_i8(tmem_base + BN, x1_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), accum);
+                    }
+                    umma_commit(smem_u32(&bars->empty[stage]));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&bars->acc_full));
+                acc_phase ^= 1;
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to this warp
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        const bool vec_ok = ((ldy & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+            ok = mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, err, 0x24);
+            if (!ok) break;
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const float us = (row < m) ? __ldg(unscale + row) : 0.0f;
+            float *yrow = y + (size_t)row * ldy;
+            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(lane_base + (uint32_t)(c * 32), r0);
+                tmem_ld_32x32(lane_base + (uint32_t)(BN + c * 32), r1);
+                tmem_ld_wait();
+                const int j0 = n0 + c * 32;
+                if (row < m && j0 < n) {
+                    if (vec_ok && j0 + 32 <= n) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            const float4 sc = __ldg(reinterpret_cast<const float4 *>(scales + j0) + v);
+                            float4 o;
+                            o.x = __fmul_rn(combine(r0[4 * v + 0], r1[4 * v + 0]) * us, sc.x);
+                            o.y = __fmul_rn(combine(r0[4 * v + 1], r1[4 * v + 1]) * us, sc.y);
+                            o.z = __fmul_rn(combine(r0[4 * v + 2], r1[4 * v + 2]) * us, sc.z);
+                            o.w = __fmul_rn(combine(r0[4 * v + 3], r1[4 * v + 3]) * us, sc.w);
+                            if (bias) {
+                                const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + j0) + v);
+                                o.x = __fadd_rn(o.x, bv.x);
+                                o.y = __fadd_rn(o.y, bv.y);
+                                o.z = __fadd_rn(o.z, bv.z);
+                                o.w = __fadd_rn(o.w, bv.w);
+                            }
+                            *reinterpret_cast<float4 *>(yrow + j0 + 4 * v) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 32; ++v) {
+                            const int j = j0 + v;
+                            if (j < n) {
+                                float o = __fmul_rn(combine(r0[v], r1[v]) * us, __ldg(scales + j));
+                                if (bias) o = __fadd_rn(o, __ldg(bias + j));
+                                yrow[j] = o;
+                            }
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
+            acc_phase ^= 1;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// Activation pre-pass: one warp per row of x [m, k] (k % 16 == 0).  Row max -> e with
+// max|x| * 2^e in [2^12, 2^13); v = rint(x * 2^e); d0 = balanced low digit in [-64, 63],
+// d1 = (v - d0) / 128 in [-64, 64].  unscale[r] = 2^-e (NaN if the row holds Inf/NaN).
+__global__ void __launch_bounds__(256)
+x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t *__restrict__ x1,
+                   float *__restrict__ unscale, int m, int k) {
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    const int n4 = k >> 2;
+    for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < m; row += warps) {
+        const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)row * k);
+        float mx = 0.0f;
+        int bad = 0;
+        for (int i = lane; i < n4; i += 32) {
+            const float4 t = __ldg(src + i);
+            const float a0 = fabsf(t.x), a1 = fabsf(t.y), a2 = fabsf(t.z), a3 = fabsf(t.w);
+            bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) | !(a2 <= 3.402823466e38f) |
+                   !(a3 <= 3.402823466e38f);
+            mx = fmaxf(fmaxf(mx, fmaxf(a0, a1)), fmaxf(a2, a3));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        bad = __any_sync(0xffffffffu, bad);
+        const int e = 12 - ((mx > 0.0f) ? ilogbf(mx) : 0);
+        const int e1 = e >> 1, e2 = e - e1;  // 2^e = 2^e1 * 2^e2, both factors finite
+        const float f1 = __int_as_float((127 + e1) << 23), f2 = __int_as_float((127 + e2) << 23);
+        if (lane == 0) {
+            const float u = __int_as_float((127 - e1) << 23) * __int_as_float((127 - e2) << 23);
+            unscale[row] = bad ? __int_as_float(0x7fc00000) : u;
+        }
+        uint32_t *d0p = reinterpret_cast<uint32_t *>(x0 + (size_t)row * k);
+        uint32_t *d1p = reinterpret_cast<uint32_t *>(x1 + (size_t)row * k);
+        for (int i = lane; i < n4; i += 32) {
+            const float4 t = __ldg(src + i);
+            const float xv[4] = {t.x, t.y, t.z, t.w};
+            uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                const int v = bad ? 0 : __float2int_rn(xv[b] * f1 * f2);
+                const int d0 = ((v + 64) & 127) - 64;
+                const int d1 = (v - d0) >> 7;
+                w0 |= (uint32_t)(d0 & 0xff) << (8 * b);
+                w1 |= (uint32_t)(d1 & 0xff) << (8 * b);
+            }
+            d0p[i] = w0;
+            d1p[i] = w1;
+        }
+    }
+}
+
+}  // namespace
+
+bool prefill_i8_supports(const nne_qlinear *ql, size_t m) {
+    if (!ql || !ql->tmap_w8) return false;
+    return m > 0 && m <= 0x7fffff00u;
+}
+
+int prefill_i8_prepare_layer(nne_qlinear *ql) {
+    ql->tmap_w8 = nullptr;
+    if (ql->n == 0 || ql->k == 0 || ql->k % 16 != 0) return NNE_OK;
+    if (ql->n > 0x7fffff00u || ql->k > 0x7fffff00u) return NNE_OK;
+    if ((reinterpret_cast<uintptr_t>(ql->q) & 15u) != 0) return NNE_OK;
+    CUtensorMap *map = new CUtensorMap;
+    int st = tma_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ql->q, ql->k, ql->n, BKB, BN,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != NNE_OK) {
+        delete map;
+        return NNE_OK;  // no tensor maps on this driver: the layer simply does not take this path
+    }
+    ql->tmap_w8 = map;
+    return NNE_OK;
+}
+
+void prefill_i8_release_layer(nne_qlinear *ql) {
+    if (ql->tmap_w8) delete static_cast<CUtensorMap *>(ql->tmap_w8);
+    ql->tmap_w8 = nullptr;
+}
+
+int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
+                      cudaStream_t s) {
+    nne_ctx *ctx = ql->ctx;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_i8_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        attr_set = true;
+    }
+    // stream-ordered workspace: two int8 digit planes [m, k] and the per-row factors [m]
+    const size_t plane = m * ql->k;
+    const size_t bytes = 2 * plane + ((m * sizeof(float) + 255) & ~(size_t)255) + 256;
+    uint8_t *ws = nullptr;
+    NNE_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void **>(&ws), bytes, s));
+    int8_t *x0 = reinterpret_cast<int8_t *>(ws);
+    int8_t *x1 = x0 + plane;
+    float *unscale = reinterpret_cast<float *>(ws + ((2 * plane + 255) & ~(size_t)255));
+    {
+        size_t blocks = (m + 7) / 8;
+        const size_t cap = (size_t)ctx->sm_count * 8;
+        if (blocks > cap) blocks = cap;
+        x_to_digits_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, x0, x1, unscale, (int)m, (int)ql->k);
+        cudaError_t e = cudaGetLastError();
+        count_launch();
+        if (e != cudaSuccess) {
+            cudaFreeAsync(ws, s);
+            return fail(NNE_ERR_CUDA, "activation pre-pass launch failed: %s", cudaGetErrorString(e));
+        }
+    }
+    CUtensorMap tmap_x0, tmap_x1;
+    int st = tma_make_map_2d(&tmap_x0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x0, ql->k, m, BKB, BM,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st == NNE_OK)
+        st = tma_make_map_2d(&tmap_x1, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x1, ql->k, m, BKB, BM,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != NNE_OK) {
+        cudaFreeAsync(ws, s);
+        return st;
+    }
+    const int tiles_m = (int)((m + BM - 1) / BM);
+    const int tiles_n = (int)((ql->n + BN - 1) / BN);
+    const long long tiles = (long long)tiles_m * tiles_n;
+    if (tiles > 0x7fffffff) {
+        cudaFreeAsync(ws, s);
+        return fail(NNE_ERR_UNSUPPORTED, "too many output tiles");
+    }
+    int grid = ctx->sm_count;
+    if (grid > tiles) grid = (int)tiles;
+    qlinear_prefill_i8_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(
+        *static_cast<const CUtensorMap *>(ql->tmap_w8), tmap_x0, tmap_x1, unscale, ql->scales,
+        ql->bias, y, (int)m, (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
+    cudaError_t e = cudaGetLastError();
+    count_launch();
+    cudaFreeAsync(ws, s);
+    if (e != cudaSuccess)
+        return fail(NNE_ERR_CUDA, "prefill kernel launch failed: %s", cudaGetErrorString(e));
+    return NNE_OK;
+}
+
+}  // namespace nne

@@ -176,4 +176,9 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Host: encodes a 2-D tiled tensor map (row-major [outer, inner], box [box_outer, box_inner]).
+int tma_make_map_2d(CUtensorMap *map, CUtensorMapDataType dt, size_t elem_bytes, const void *base,
+                    size_t inner, size_t outer, uint32_t box_inner, uint32_t box_outer,
+                    CUtensorMapSwizzle sw);
+
 }  // namespace nne

@@ -36,11 +36,23 @@ def test_static_forward_matches_ordinary_forward_twice(nne, ctx):
         torch.cuda.synchronize()
         ctx.check()
         a, r = y_new.cpu().numpy(), y_ref.cpu().numpy()
-        assert ql.kernel_for(m) == 2          # the ordinary forward took the same kernel
-        assert np.array_equal(a.view(np.uint32), r.view(np.uint32))
+        assert ql.kernel_for(m) == 2          # the ordinary forward took a tensor-core kernel too
+        # Same contraction, two tensor-core kernels: this entry point runs the bf16 one (codes
+        # dequantized to bf16 in shared memory, x rounded to bf16), the ordinary forward the
+        # integer one.  They must agree within the tolerance of the forward tests,
+        # tol_j = 1e-3 * ||x||inf * scale_j * sum_k |q_jk|, and so must each with the oracle.
         tol, _ = oracle.tolerance(ql.qweight.reshape(n, k), ql.scales, x)
         y_oracle = oracle.forward(ql.qweight.reshape(n, k), ql.scales, b, x)
-        assert float((np.abs(a - y_oracle) / tol).max()) <= 1.0   # tolerance of the forward tests
+        assert float((np.abs(a - r) / tol).max()) <= 1.0
+        assert float((np.abs(a - y_oracle) / tol).max()) <= 1.0
+        assert float((np.abs(r - y_oracle) / tol).max()) <= 1.0
+        # with integer-valued activations every kernel is exact, so there the two agree bit for bit
+        xi = np.random.default_rng(call).integers(-8, 9, size=(m, k)).astype(np.float32)
+        xid = torch.from_numpy(xi).cuda()
+        assert lib.nne_qlinear_forward_dev(ql._handle, xid.data_ptr(), m, k, y_ref.data_ptr(), s) == 0
+        assert lib.nne_qlinear_forward_dev_static(ql._handle, xid.data_ptr(), m, k, y_new.data_ptr(), s) == 0
+        torch.cuda.synchronize()
+        assert np.array_equal(y_new.cpu().numpy().view(np.uint32), y_ref.cpu().numpy().view(np.uint32))
 
 
 def test_static_forward_refuses_what_it_cannot_take(nne, ctx):
