@@ -254,20 +254,37 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
 }
 
-// Activation pre-pass: one warp per row of x [m, k] (k % 16 == 0).  Row max -> e with
-// max|x| * 2^e in [2^12, 2^13); v = rint(x * 2^e); d0 = balanced low digit in [-64, 63],
-// d1 = (v - d0) / 128 in [-64, 64].  unscale[r] = 2^-e (NaN if the row holds Inf/NaN).
+// Activation pre-pass: one CTA of 256 threads per row of x [m, k] (k % 16 == 0).  Row max -> e
+// with max|x| * 2^e in [2^12, 2^13); v = rint(x * 2^e); d0 = balanced low digit in [-64, 63],
+// d1 = (v - d0) / 128 in [-64, 64].  unscale[r] = 2^-e (NaN if the row holds Inf/NaN).  The row
+// is read from memory once: each thread keeps up to 8 float4 of it in registers between the two
+// passes (k <= 8192); longer rows re-read the rest.
 __global__ void __launch_bounds__(256)
 x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t *__restrict__ x1,
                    float *__restrict__ unscale, int m, int k) {
-    const int lane = threadIdx.x & 31;
-    const int warps = gridDim.x * (blockDim.x >> 5);
+    __shared__ float wmax[8];
+    __shared__ int wbad[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n4 = k >> 2;
-    for (int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < m; row += warps) {
+    for (int row = blockIdx.x; row < m; row += gridDim.x) {
         const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)row * k);
+        float4 keep[8];
         float mx = 0.0f;
         int bad = 0;
-        for (int i = lane; i < n4; i += 32) {
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = tid + u * 256;
+            keep[u] = (i < n4) ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float a0 = fabsf(keep[u].x), a1 = fabsf(keep[u].y), a2 = fabsf(keep[u].z),
+                        a3 = fabsf(keep[u].w);
+            bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) | !(a2 <= 3.402823466e38f) |
+                   !(a3 <= 3.402823466e38f);
+            mx = fmaxf(fmaxf(mx, fmaxf(a0, a1)), fmaxf(a2, a3));
+        }
+        for (int i = tid + 2048; i < n4; i += 256) {
             const float4 t = __ldg(src + i);
             const float a0 = fabsf(t.x), a1 = fabsf(t.y), a2 = fabsf(t.z), a3 = fabsf(t.w);
             bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) | !(a2 <= 3.402823466e38f) |
@@ -277,17 +294,29 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
         bad = __any_sync(0xffffffffu, bad);
+        __syncthreads();  // the previous row's readers of wmax/wbad are done
+        if (lane == 0) {
+            wmax[warp] = mx;
+            wbad[warp] = bad;
+        }
+        __syncthreads();
+        mx = 0.0f;
+        bad = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            mx = fmaxf(mx, wmax[w]);
+            bad |= wbad[w];
+        }
         const int e = 12 - ((mx > 0.0f) ? ilogbf(mx) : 0);
         const int e1 = e >> 1, e2 = e - e1;  // 2^e = 2^e1 * 2^e2, both factors finite
         const float f1 = __int_as_float((127 + e1) << 23), f2 = __int_as_float((127 + e2) << 23);
-        if (lane == 0) {
+        if (tid == 0) {
             const float u = __int_as_float((127 - e1) << 23) * __int_as_float((127 - e2) << 23);
             unscale[row] = bad ? __int_as_float(0x7fc00000) : u;
         }
         uint32_t *d0p = reinterpret_cast<uint32_t *>(x0 + (size_t)row * k);
         uint32_t *d1p = reinterpret_cast<uint32_t *>(x1 + (size_t)row * k);
-        for (int i = lane; i < n4; i += 32) {
-            const float4 t = __ldg(src + i);
+        auto emit = [&](int i, const float4 &t) {
             const float xv[4] = {t.x, t.y, t.z, t.w};
             uint32_t w0 = 0u, w1 = 0u;
 #pragma unroll
@@ -300,7 +329,13 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
             }
             d0p[i] = w0;
             d1p[i] = w1;
+        };
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = tid + u * 256;
+            if (i < n4) emit(i, keep[u]);
         }
+        for (int i = tid + 2048; i < n4; i += 256) emit(i, __ldg(src + i));
     }
 }
 
@@ -350,8 +385,8 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
     int8_t *x1 = x0 + plane;
     float *unscale = reinterpret_cast<float *>(ws + ((2 * plane + 255) & ~(size_t)255));
     {
-        size_t blocks = (m + 7) / 8;
-        const size_t cap = (size_t)ctx->sm_count * 8;
+        size_t blocks = m;
+        const size_t cap = (size_t)ctx->sm_count * 32;
         if (blocks > cap) blocks = cap;
         x_to_digits_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, x0, x1, unscale, (int)m, (int)ql->k);
         cudaError_t e = cudaGetLastError();
