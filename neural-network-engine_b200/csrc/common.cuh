@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
 #include <atomic>
 #include <mutex>
 #include <string>
@@ -50,6 +51,15 @@ int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)))
 
 // ---- launch counter ----------------------------------------------------------------------
 extern std::atomic<uint64_t> g_launches;
+// Programmatic dependent launch is on unless NNE_PDL=0.
+inline bool pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char *e = getenv("NNE_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
 inline void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed); }
 
 // Checks the launch that was just issued.

@@ -469,15 +469,6 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
     }
 }
 
-bool pdl_enabled() {
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("NNE_PDL");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
-}
-
 template <int MT>
 int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot_bytes, int kpad,
                      int sb_rows, int bufs, size_t smem, int grid, cudaStream_t s) {

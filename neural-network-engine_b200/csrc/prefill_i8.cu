@@ -19,7 +19,8 @@
 //   warp 0      TMA producer: int8 weight tile [256 x 128] and the two activation digit tiles
 //               [128 x 128], all 128B-swizzled straight into the UMMA K-major layout; no multicast
 //   warp 1      one thread issues 2 x 4 tcgen05.mma (128x256x32, kind::i8) and tcgen05.commit
-//   warps 2-5   epilogue: tcgen05.ld of both accumulators, combine, scale, bias, f32 store
+//   warps 2-9   epilogue: tcgen05.ld of both accumulators, combine, transpose through shared
+//               memory, scale, bias, coalesced f32 stores
 // Every mbarrier wait is bounded (~2 s): on expiry the context's device error word is set and the
 // CTA drains, frees its TMEM and returns.
 #include <cuda.h>
@@ -36,8 +37,9 @@ constexpr int W_BYTES = BN * BKB;   // 32 KB
 constexpr int X_BYTES = BM * BKB;   // 16 KB per digit
 constexpr int STAGE_BYTES = W_BYTES + 2 * X_BYTES;  // 64 KB
 constexpr int BAR_BYTES = 256;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + BAR_BYTES + 1024;
-constexpr int NUM_EPI_WARPS = 4;
+constexpr int NUM_EPI_WARPS = 8;  // two per TMEM lane quarter, each takes half of the columns
+constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;  // one 32x32 f32 block per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_EPI_WARPS * EPI_STAGE_BYTES + BAR_BYTES + 1024;
 constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
 constexpr uint32_t TMEM_COLS = 512;  // two int32 accumulators of 256 columns
 
@@ -66,9 +68,17 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
         : "memory");
 }
 
-// D0 + 128*D1 as one correctly rounded float (the int64 sum is exact).
+// D0 + 128*D1 as one correctly rounded float, without a 64-bit integer or an int->float
+// conversion (both are slow-rate instructions): split the sum as top * 2^20 + lo with
+// |top| < 2^19 + 2^11 and 0 <= lo < 2^21, turn each part into a float exactly by adding it to the
+// bit pattern of 1.5 * 2^23, and let one fused multiply-add round once.
 __device__ __forceinline__ float combine(uint32_t d0, uint32_t d1) {
-    return __ll2float_rn((long long)(int)d0 + ((long long)(int)d1 << 7));
+    const int b = (int)d0, a = (int)d1;
+    const int top = (b >> 20) + (a >> 13);
+    const int lo = (b & 0xFFFFF) + ((a & 0x1FFF) << 7);
+    const float ft = __int_as_float(0x4B400000 + top) - 12582912.0f;
+    const float fl = __int_as_float(0x4B400000 + lo) - 12582912.0f;
+    return fmaf(ft, 1048576.0f, fl);
 }
 
 struct Bars {
@@ -91,7 +101,8 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    Bars *bars = reinterpret_cast<Bars *>(smem + STAGES * STAGE_BYTES);
+    uint8_t *epi_smem = smem + STAGES * STAGE_BYTES;
+    Bars *bars = reinterpret_cast<Bars *>(epi_smem + NUM_EPI_WARPS * EPI_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (k + BKB - 1) / BKB;
     volatile int *abort_flag = &bars->abort_flag;
@@ -117,6 +128,7 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
+    grid_launch_dependents();  // the next kernel's prologue may overlap this one
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -124,15 +136,32 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // Weights never change after the layer is created, so the first ring of weight
+            // tiles is requested before waiting for the pre-pass (the previous kernel in the
+            // stream under programmatic dependent launch) that writes the digit planes.
+            int pre = 0;
+            if ((int)blockIdx.x < num_tiles) {
+                const int n_first = ((int)blockIdx.x / tiles_m) * BN;
+                for (; pre < STAGES && pre < num_kb; ++pre) {
+                    const uint32_t full = smem_u32(&bars->full[pre]);
+                    mbar_arrive_expect_tx(full, STAGE_BYTES);
+                    tma_load_2d(smem_u32(smem + pre * STAGE_BYTES), &tmap_w, pre * BKB, n_first, full);
+                }
+            }
+            grid_dependency_wait();
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, err, 0x21);
-                    if (!ok) break;
                     uint8_t *st = smem + stage * STAGE_BYTES;
                     const uint32_t full = smem_u32(&bars->full[stage]);
-                    mbar_arrive_expect_tx(full, STAGE_BYTES);
-                    tma_load_2d(smem_u32(st), &tmap_w, kb * BKB, n0, full);
+                    if (pre > 0) {
+                        --pre;  // slot still empty from the start; its weight tile is on the way
+                    } else {
+                        ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, err, 0x21);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(full, STAGE_BYTES);
+                        tma_load_2d(smem_u32(st), &tmap_w, kb * BKB, n0, full);
+                    }
                     tma_load_2d(smem_u32(st + W_BYTES), &tmap_x0, kb * BKB, m0, full);
                     tma_load_2d(smem_u32(st + W_BYTES + X_BYTES), &tmap_x1, kb * BKB, m0, full);
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -185,62 +214,95 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
         }
     } else {
         // ---------------- epilogue ----------------
-        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to this warp
+        // Warp (quarter, half) drains TMEM lanes [32*quarter, +32) x columns [128*half, +128) of
+        // both accumulators in four 32-column chunks.  A chunk arrives with lane = output row;
+        // it is combined and multiplied by the row's 2^-e there, transposed through a 4 KB
+        // shared block (float4 slots XOR-swizzled by row: conflict free both ways), and leaves
+        // with 8 lanes per output row, so each store instruction writes four full 128-byte lines
+        // and the channel's scale and bias are loaded once per chunk.
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        float4 *stg = reinterpret_cast<float4 *>(epi_smem + (warp - 2) * EPI_STAGE_BYTES);
         uint32_t acc_phase = 0;
         bool ok = true;
         const bool vec_ok = ((ldy & 3) == 0) && ((reinterpret_cast<uintptr_t>(y) & 15) == 0);
+        const int c4 = lane & 7, rsub = lane >> 3;
+        grid_dependency_wait();  // unscale[] is written by the pre-pass
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
             const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
+            const int row0 = m0 + quarter * 32;
+            const int row = row0 + lane;
+            const float us = (row < m) ? __ldg(unscale + row) : 0.0f;
             ok = mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, err, 0x24);
             if (!ok) break;
             tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
-            const float us = (row < m) ? __ldg(unscale + row) : 0.0f;
-            float *yrow = y + (size_t)row * ldy;
-            const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r0[32], r1[32];
-                tmem_ld_32x32(lane_base + (uint32_t)(c * 32), r0);
-                tmem_ld_32x32(lane_base + (uint32_t)(BN + c * 32), r1);
+            const uint32_t lane_base =
+                tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(half * (BN / 2));
+            // Drain: this warp's 128 columns of both accumulators become 128 floats in
+            // registers, and TMEM goes back to the MMA warp before anything is stored.
+            float f[BN / 2];
+#pragma unroll
+            for (int g = 0; g < BN / 32; ++g) {
+                uint32_t r0[16], r1[16];
+                tmem_ld_32x16(lane_base + (uint32_t)(g * 16), r0);
+                tmem_ld_32x16(lane_base + (uint32_t)(BN + g * 16), r1);
                 tmem_ld_wait();
-                const int j0 = n0 + c * 32;
-                if (row < m && j0 < n) {
-                    if (vec_ok && j0 + 32 <= n) {
 #pragma unroll
-                        for (int v = 0; v < 8; ++v) {
-                            const float4 sc = __ldg(reinterpret_cast<const float4 *>(scales + j0) + v);
-                            float4 o;
-                            o.x = __fmul_rn(combine(r0[4 * v + 0], r1[4 * v + 0]) * us, sc.x);
-                            o.y = __fmul_rn(combine(r0[4 * v + 1], r1[4 * v + 1]) * us, sc.y);
-                            o.z = __fmul_rn(combine(r0[4 * v + 2], r1[4 * v + 2]) * us, sc.z);
-                            o.w = __fmul_rn(combine(r0[4 * v + 3], r1[4 * v + 3]) * us, sc.w);
-                            if (bias) {
-                                const float4 bv = __ldg(reinterpret_cast<const float4 *>(bias + j0) + v);
-                                o.x = __fadd_rn(o.x, bv.x);
-                                o.y = __fadd_rn(o.y, bv.y);
-                                o.z = __fadd_rn(o.z, bv.z);
-                                o.w = __fadd_rn(o.w, bv.w);
-                            }
-                            *reinterpret_cast<float4 *>(yrow + j0 + 4 * v) = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < 32; ++v) {
-                            const int j = j0 + v;
-                            if (j < n) {
-                                float o = __fmul_rn(combine(r0[v], r1[v]) * us, __ldg(scales + j));
-                                if (bias) o = __fadd_rn(o, __ldg(bias + j));
-                                yrow[j] = o;
-                            }
-                        }
-                    }
-                }
+                for (int v = 0; v < 16; ++v) f[g * 16 + v] = combine(r0[v], r1[v]);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty));
             acc_phase ^= 1;
+#pragma unroll
+            for (int ci = 0; ci < BN / 64; ++ci) {
+                const int j0 = n0 + half * (BN / 2) + ci * 32;
+                if (j0 >= n) continue;
+                if (vec_ok && j0 + 32 <= n) {
+#pragma unroll
+                    for (int v = 0; v < 8; ++v) {
+                        float4 o;
+                        o.x = f[ci * 32 + 4 * v + 0] * us;
+                        o.y = f[ci * 32 + 4 * v + 1] * us;
+                        o.z = f[ci * 32 + 4 * v + 2] * us;
+                        o.w = f[ci * 32 + 4 * v + 3] * us;
+                        stg[lane * 8 + (v ^ (lane & 7))] = o;
+                    }
+                    __syncwarp();
+                    const float4 sc = __ldg(reinterpret_cast<const float4 *>(scales + j0) + c4);
+                    float4 bv = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (bias) bv = __ldg(reinterpret_cast<const float4 *>(bias + j0) + c4);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rr = i * 4 + rsub;
+                        float4 o = stg[rr * 8 + (c4 ^ (rr & 7))];
+                        o.x = __fmul_rn(o.x, sc.x);
+                        o.y = __fmul_rn(o.y, sc.y);
+                        o.z = __fmul_rn(o.z, sc.z);
+                        o.w = __fmul_rn(o.w, sc.w);
+                        if (bias) {
+                            o.x = __fadd_rn(o.x, bv.x);
+                            o.y = __fadd_rn(o.y, bv.y);
+                            o.z = __fadd_rn(o.z, bv.z);
+                            o.w = __fadd_rn(o.w, bv.w);
+                        }
+                        if (row0 + rr < m)
+                            *reinterpret_cast<float4 *>(y + (size_t)(row0 + rr) * ldy + j0 + 4 * c4) = o;
+                    }
+                    __syncwarp();  // the block is rewritten by the next chunk
+                } else if (row < m) {
+                    float *yrow = y + (size_t)row * ldy;
+#pragma unroll
+                    for (int v = 0; v < 32; ++v) {
+                        const int j = j0 + v;
+                        if (j < n) {
+                            float o = __fmul_rn(f[ci * 32 + v] * us, __ldg(scales + j));
+                            if (bias) o = __fadd_rn(o, __ldg(bias + j));
+                            yrow[j] = o;
+                        }
+                    }
+                }
+            }
         }
     }
 
@@ -266,6 +328,10 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
     __shared__ int wbad[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int n4 = k >> 2;
+    // x may be the output of the previous kernel in the stream, and the digit planes may still
+    // be read by it: nothing is touched before that kernel has finished.
+    grid_dependency_wait();
+    grid_launch_dependents();
     for (int row = blockIdx.x; row < m; row += gridDim.x) {
         const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)row * k);
         float4 keep[8];
@@ -381,6 +447,9 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
     const size_t bytes = 2 * plane + ((m * sizeof(float) + 255) & ~(size_t)255) + 256;
     uint8_t *ws = nullptr;
     NNE_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void **>(&ws), bytes, s));
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
     int8_t *x0 = reinterpret_cast<int8_t *>(ws);
     int8_t *x1 = x0 + plane;
     float *unscale = reinterpret_cast<float *>(ws + ((2 * plane + 255) & ~(size_t)255));
@@ -388,8 +457,13 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
         size_t blocks = m;
         const size_t cap = (size_t)ctx->sm_count * 32;
         if (blocks > cap) blocks = cap;
-        x_to_digits_kernel<<<(unsigned)blocks, 256, 0, s>>>(x, x0, x1, unscale, (int)m, (int)ql->k);
-        cudaError_t e = cudaGetLastError();
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)blocks);
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cfg.attrs = pdl;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, x_to_digits_kernel, x, x0, x1, unscale, (int)m, (int)ql->k);
         count_launch();
         if (e != cudaSuccess) {
             cudaFreeAsync(ws, s);
@@ -415,10 +489,17 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
     }
     int grid = ctx->sm_count;
     if (grid > tiles) grid = (int)tiles;
-    qlinear_prefill_i8_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(
-        *static_cast<const CUtensorMap *>(ql->tmap_w8), tmap_x0, tmap_x1, unscale, ql->scales,
-        ql->bias, y, (int)m, (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
-    cudaError_t e = cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = s;
+    cfg.attrs = pdl;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(
+        &cfg, qlinear_prefill_i8_kernel, *static_cast<const CUtensorMap *>(ql->tmap_w8), tmap_x0,
+        tmap_x1, (const float *)unscale, (const float *)ql->scales, (const float *)ql->bias, y, (int)m,
+        (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
     count_launch();
     cudaFreeAsync(ws, s);
     if (e != cudaSuccess)
