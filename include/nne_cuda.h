@@ -183,7 +183,9 @@ NNE_API int nne_qlinear_plan_launches(const nne_plan *plan);
 
 /* Which kernel a forward of m rows on this layer dispatches to: 1 = streaming GEMV (small m),
  * 2 = tcgen05/TMEM tensor-core kernel (integer form; NNE_PREFILL=bf16 in the environment selects
- * the bf16 form), 3 = generic kernel for shapes the others do not take. */
+ * the bf16 form), 3 = generic kernel for shapes the others do not take, 4 = small-batch
+ * tensor-core kernel (3 <= m <= 16: int8 weights as the MMA's M side, read once; bit-identical per
+ * row to kernel 1; NNE_SKINNY=0 in the environment sends these sizes to kernel 1 instead). */
 NNE_API int nne_qlinear_kernel_for(const nne_qlinear *ql, size_t m);
 /* Number of kernels this library has launched in the calling process (all contexts). */
 NNE_API uint64_t nne_launch_count(void);

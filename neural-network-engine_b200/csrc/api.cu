@@ -96,10 +96,21 @@ bool prefill_bf16_forced() {
     return v;
 }
 
-// Kernel choice for a forward of m rows.  1 = streaming GEMV, 2 = tensor-core, 3 = generic.
+// NNE_SKINNY=0 sends 3..16-row forwards through the streaming GEMV in passes of two rows.
+bool skinny_disabled() {
+    static const bool v = []() {
+        const char *e = getenv("NNE_SKINNY");
+        return e && e[0] == '0';
+    }();
+    return v;
+}
+
+// Kernel choice for a forward of m rows.  1 = streaming GEMV, 2 = tensor-core, 3 = generic,
+// 4 = small-batch tensor-core.
 int pick_kernel(const nne_qlinear *ql, size_t m, const float *x, const float *y) {
     const bool base_ok = aligned(ql->q, 16) && (x == nullptr || aligned(x, 16)) &&
                          (y == nullptr || aligned(y, 4));
+    if (base_ok && skinny_supports(ql, m) && !skinny_disabled()) return 4;
     if (m > 16 && base_ok && (prefill_i8_supports(ql, m) || prefill_supports(ql, m))) return 2;
     if (base_ok && gemv_supports(ql->n, ql->k, m)) return 1;
     return 3;
@@ -125,6 +136,8 @@ int forward_dev(nne_qlinear *ql, const float *x, size_t m, size_t k, float *y, s
         case 2:
             if (prefill_i8_supports(ql, m) && !prefill_bf16_forced()) return launch_prefill_i8(ql, x, y, m, ldy, s);
             return launch_prefill(ql, x, y, m, ldy, s);
+        case 4:
+            return launch_skinny(ql, x, y, m, ldy, s);
         case 1:
             return launch_gemv(ql->ctx, ql->q, ql->scales, ql->bias, x, y, ql->n, ql->k, m, ldy, s);
         default:
@@ -402,6 +415,7 @@ int nne_qlinear_create_from_f32_dev(nne_ctx *ctx, const float *w_dev, const floa
     }
     if (st == NNE_OK) st = prefill_prepare_layer(ql);
     if (st == NNE_OK) st = prefill_i8_prepare_layer(ql);
+    if (st == NNE_OK) st = skinny_prepare_layer(ql);
     if (st != NNE_OK) {
         nne_qlinear_destroy(ql);
         return st;
@@ -442,6 +456,7 @@ int nne_qlinear_create_from_f32(nne_ctx *ctx, const float *w_host, const float *
     }
     if (st == NNE_OK) st = prefill_prepare_layer(ql);
     if (st == NNE_OK) st = prefill_i8_prepare_layer(ql);
+    if (st == NNE_OK) st = skinny_prepare_layer(ql);
     if (st != NNE_OK) {
         nne_qlinear_destroy(ql);
         return st;
@@ -480,6 +495,7 @@ int nne_qlinear_create_from_i8(nne_ctx *ctx, const int8_t *q_host, const float *
     if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "layer upload failed: %s", cudaGetErrorString(e));
     if (st == NNE_OK) st = prefill_prepare_layer(ql);
     if (st == NNE_OK) st = prefill_i8_prepare_layer(ql);
+    if (st == NNE_OK) st = skinny_prepare_layer(ql);
     if (st != NNE_OK) {
         nne_qlinear_destroy(ql);
         return st;
@@ -495,6 +511,7 @@ int nne_qlinear_destroy(nne_qlinear *ql) {
     cudaSetDevice(ql->device);
     prefill_release_layer(ql);
     prefill_i8_release_layer(ql);
+    skinny_release_layer(ql);
     if (ql->own) {
         if (ql->q) cudaFree(ql->q);
         if (ql->scales) cudaFree(ql->scales);

@@ -106,6 +106,7 @@ struct nne_qlinear {
     bool own = true;
     void *tmap_w = nullptr;   // host copy of the TMA descriptor of q (bf16 tensor path), or null
     void *tmap_w8 = nullptr;  // host copy of the swizzled TMA descriptor of q (int8 tensor path)
+    void *tmap_wsk = nullptr; // same with 128-row boxes (small-batch tensor path)
 };
 
 namespace nne {
@@ -166,6 +167,10 @@ int prefill_prepare_layer(nne_qlinear *ql);  // builds the weight TMA descriptor
 void prefill_release_layer(nne_qlinear *ql);
 int launch_prefill(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
                    cudaStream_t s);
+bool skinny_supports(const nne_qlinear *ql, size_t m);
+int skinny_prepare_layer(nne_qlinear *ql);
+void skinny_release_layer(nne_qlinear *ql);
+int launch_skinny(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy, cudaStream_t s);
 bool prefill_i8_supports(const nne_qlinear *ql, size_t m);
 int prefill_i8_prepare_layer(nne_qlinear *ql);
 void prefill_i8_release_layer(nne_qlinear *ql);

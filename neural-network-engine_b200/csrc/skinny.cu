@@ -1,0 +1,535 @@
+// QLinear::forward for small batches, 3 <= m <= 16 (reference: src/nn/quantized.rs:176-194), as an
+// integer tensor-core kernel that reads the int8 weights exactly once.
+//
+// The weights are the M side of the MMA (128 output channels per tile), the activations the N
+// side: the m rows of x go to the same fixed-point grid as in the streaming GEMV
+// (v = rint(x * 2^e), |v| <= 2^20, e from the row's largest |x|; three balanced base-128 int8
+// digits), stacked as 48 "rows" (digit d of activation row r = row 16 d + r).  One
+// tcgen05.mma.kind::i8 of shape 128 x 48 x 32 therefore multiplies 4 KB of weights with all three
+// digit planes of all 16 rows, and the int32 accumulators in TMEM hold EXACT integer sums.  With
+// the same grid and the same final expression, the result for an activation row is bit-identical
+// to what the streaming GEMV gives for that row alone.
+//
+// A layer has fewer 128-channel tiles than the GPU has SMs, so the (tile, k-block) units are cut
+// into one contiguous range per CTA.  A CTA that owns a whole tile writes y itself; otherwise it
+// adds its exact int64 partial sums into a zeroed workspace with integer atomics (order
+// independent, so the result does not depend on timing) and the last CTA to finish a tile turns
+// the sums into y.
+//
+// Warp roles per CTA (192 threads, 1 CTA per SM):
+//   warp 0      TMA producer: 16 KB weight tile + 6 KB digit tile per unit into an 8-slot ring,
+//               SWIZZLE_128B, weights with an L2 evict-first hint
+//   warp 1      one lane issues 4 tcgen05.mma per unit and commits to the slot's mbarrier
+//   warps 2-5   epilogue: tcgen05.ld (TMEM lane = output channel), combine the digits, then either
+//               finalize or atomically add
+// The pre-pass kernel (digits of x, per-row 2^-e, zeroing of the workspace) runs just before and
+// the two are chained with programmatic dependent launch: the weight ring fills while the
+// pre-pass runs.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace nne {
+namespace {
+
+constexpr int SK_BM = 128;    // output channels per tile
+constexpr int SK_BKB = 128;   // bytes (= int8 elements) of K per unit
+constexpr int SK_ROWS = 16;   // activation rows (padded)
+constexpr int SK_N = 48;      // MMA N: 3 digit planes x 16 rows
+constexpr int SK_W_BYTES = SK_BM * SK_BKB;  // 16 KB
+constexpr int SK_X_BYTES = SK_N * SK_BKB;   // 6 KB
+constexpr int SK_STAGE_BYTES = SK_W_BYTES + SK_X_BYTES;  // 22 KB, a multiple of 1024
+constexpr int SK_STAGES = 8;
+constexpr int SK_BAR_BYTES = 256;
+constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + SK_BAR_BYTES + 1024;
+constexpr int SK_THREADS = 192;
+constexpr uint32_t SK_TMEM_COLS = 128;  // two accumulators of 64 columns (48 used)
+static_assert(SK_STAGE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+
+__device__ __forceinline__ uint64_t sk_desc(uint32_t smem_addr) {  // K-major, SWIZZLE_128B
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;  // 8 rows * 128 B between row groups
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// D = s32, A = B = signed int8, both K-major, M = 128, N = 48.
+constexpr uint32_t SK_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(SK_N >> 3) << 17) |
+                              ((uint32_t)(SK_BM >> 4) << 24);
+
+__device__ __forceinline__ void sk_umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(SK_IDESC), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                                 uint32_t bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+        "l"(map), "r"(c0), "r"(c1), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+struct SkBars {
+    uint64_t full[SK_STAGES];
+    uint64_t empty[SK_STAGES];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+static_assert(sizeof(SkBars) <= SK_BAR_BYTES, "barrier block too large");
+
+// Unit range of CTA b of g: contiguous, as equal as the count allows.
+__host__ __device__ inline void sk_range(long long total, int b, int g, long long &u0, long long &u1) {
+    const long long base = total / g, rem = total % g;
+    u0 = b * base + (b < rem ? b : rem);
+    u1 = u0 + base + (b < rem ? 1 : 0);
+}
+// The CTA whose range holds unit u.
+__host__ __device__ inline int sk_cta_of(long long total, int g, long long u) {
+    const long long base = total / g, rem = total % g;
+    const long long split = rem * (base + 1);
+    if (u < split) return (int)(u / (base + 1));
+    return (int)(rem + (u - split) / base);
+}
+
+struct SkWork {
+    long long *sums;     // [tiles][16][128] exact partial sums, zeroed by the pre-pass
+    int *arrivals;       // [tiles][4] partial sums delivered so far per lane quarter, zeroed by the pre-pass
+    const float *unscale;  // [16][2]: 2^-e of each row as two factors (NaN for a row with Inf/NaN)
+};
+
+__device__ __forceinline__ float sk_finish(long long s, float u0, float u1, float scale) {
+    const float dot = (float)((double)s * (double)u0 * (double)u1);  // exact product, one rounding
+    return __fmul_rn(dot, scale);
+}
+
+__global__ void __launch_bounds__(SK_THREADS, 1)
+qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
+                         const __grid_constant__ CUtensorMap tmap_x, SkWork work,
+                         const float *__restrict__ scales, const float *__restrict__ bias,
+                         float *__restrict__ y, int m, int n, int k, size_t ldy, int *err) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    SkBars *bars = reinterpret_cast<SkBars *>(smem + SK_STAGES * SK_STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_kb = (k + SK_BKB - 1) / SK_BKB;
+    const int tiles = (n + SK_BM - 1) / SK_BM;
+    const long long total = (long long)tiles * num_kb;
+    long long u0, u1;
+    sk_range(total, (int)blockIdx.x, (int)gridDim.x, u0, u1);
+    volatile int *abort_flag = &bars->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SK_STAGES; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bars->acc_full[b]), 1);
+            mbar_init(smem_u32(&bars->acc_empty[b]), 4);
+        }
+        bars->abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&bars->tmem_base)),
+                     "r"(SK_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+    grid_launch_dependents();
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+            // Weights never change after the layer is created: the ring's first round of weight
+            // tiles is requested before waiting for the pre-pass that writes the digit planes.
+            int pre = 0;
+            for (; pre < SK_STAGES && u0 + pre < u1; ++pre) {
+                const long long u = u0 + pre;
+                const int tile = (int)(u / num_kb), kb = (int)(u % num_kb);
+                const uint32_t full = smem_u32(&bars->full[pre]);
+                mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
+                tma_load_2d_hint(smem_u32(smem + pre * SK_STAGE_BYTES), &tmap_w, kb * SK_BKB,
+                                 tile * SK_BM, full, pol_w);
+            }
+            grid_dependency_wait();
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (long long u = u0; u < u1; ++u) {
+                const int tile = (int)(u / num_kb), kb = (int)(u % num_kb);
+                uint8_t *st = smem + stage * SK_STAGE_BYTES;
+                const uint32_t full = smem_u32(&bars->full[stage]);
+                if (pre > 0) {
+                    --pre;
+                } else {
+                    ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, err, 0x31);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
+                    tma_load_2d_hint(smem_u32(st), &tmap_w, kb * SK_BKB, tile * SK_BM, full, pol_w);
+                }
+                tma_load_2d_hint(smem_u32(st + SK_W_BYTES), &tmap_x, kb * SK_BKB, 0, full, pol_x);
+                if (++stage == SK_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) {
+                // Gave up: let copies that are still in flight land before the CTA exits.
+                for (int s = 0; s < SK_STAGES; ++s) {
+                    const unsigned long long t0 = globaltimer_ns();
+                    while (!mbar_try_wait(smem_u32(&bars->full[s]), 0) &&
+                           !mbar_try_wait(smem_u32(&bars->full[s]), 1) &&
+                           globaltimer_ns() - t0 < 100000000ull) {
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int seg = 0;
+            bool ok = true;
+            long long u = u0;
+            while (u < u1 && ok) {
+                const int tile = (int)(u / num_kb);
+                long long seg_end = (long long)(tile + 1) * num_kb;
+                if (seg_end > u1) seg_end = u1;
+                const int buf = seg & 1;
+                ok = mbar_wait(smem_u32(&bars->acc_empty[buf]), (uint32_t)(((seg >> 1) & 1) ^ 1),
+                               abort_flag, err, 0x32);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(buf * 64);
+                bool first = true;
+                for (; u < seg_end; ++u) {
+                    ok = mbar_wait(smem_u32(&bars->full[stage]), phase, abort_flag, err, 0x33);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint8_t *st = smem + stage * SK_STAGE_BYTES;
+                    const uint64_t w_desc = sk_desc(smem_u32(st));
+                    const uint64_t x_desc = sk_desc(smem_u32(st + SK_W_BYTES));
+#pragma unroll
+                    for (int kk = 0; kk < SK_BKB / 32; ++kk) {
+                        sk_umma(d_tmem, w_desc + (uint64_t)(kk * 2), x_desc + (uint64_t)(kk * 2),
+                                (first && kk == 0) ? 0u : 1u);
+                    }
+                    first = false;
+                    umma_commit(smem_u32(&bars->empty[stage]));
+                    if (++stage == SK_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&bars->acc_full[buf]));
+                ++seg;
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        grid_dependency_wait();  // unscale[], sums[] and arrivals[] are written by the pre-pass
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, +32) belong to this warp
+        const int ch_in_tile = quarter * 32 + lane;
+        int seg = 0;
+        bool ok = true;
+        long long u = u0;
+        while (u < u1 && ok) {
+            const int tile = (int)(u / num_kb);
+            const long long tile_u0 = (long long)tile * num_kb, tile_u1 = tile_u0 + num_kb;
+            const long long seg_end = tile_u1 < u1 ? tile_u1 : u1;
+            const bool whole = (u == tile_u0) && (seg_end == tile_u1);
+            const int buf = seg & 1;
+            ok = mbar_wait(smem_u32(&bars->acc_full[buf]), (uint32_t)((seg >> 1) & 1), abort_flag, err,
+                           0x34);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 64);
+            uint32_t d0[16], d1[16], d2[16];
+            tmem_ld_32x16(taddr, d0);
+            tmem_ld_32x16(taddr + 16, d1);
+            tmem_ld_32x16(taddr + 32, d2);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[buf]));
+
+            const int ch = tile * SK_BM + ch_in_tile;
+            long long s[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r)
+                s[r] = (long long)(int)d0[r] + ((long long)(int)d1[r] << 7) + ((long long)(int)d2[r] << 14);
+
+            bool finish = whole;
+            if (!whole) {
+                long long *dst = work.sums + ((size_t)tile * SK_ROWS) * SK_BM + ch_in_tile;
+#pragma unroll
+                for (int r = 0; r < 16; ++r)
+                    if (r < m)
+                        atomicAdd(reinterpret_cast<unsigned long long *>(dst + r * SK_BM),
+                                  (unsigned long long)s[r]);
+                // Each warp keeps its own count per (tile, lane quarter): no rendezvous between
+                // the epilogue warps.  The fence orders this warp's additions before its ticket.
+                __threadfence();
+                __syncwarp();
+                int last = 0;
+                if (lane == 0) {
+                    const int parts = sk_cta_of(total, (int)gridDim.x, tile_u1 - 1) -
+                                      sk_cta_of(total, (int)gridDim.x, tile_u0) + 1;
+                    const int ticket = atomicAdd(work.arrivals + tile * 4 + quarter, 1);
+                    last = (ticket == parts - 1) ? 1 : 0;
+                    __threadfence();
+                }
+                finish = __shfl_sync(0xffffffffu, last, 0) != 0;
+                if (finish) {
+#pragma unroll
+                    for (int r = 0; r < 16; ++r)
+                        if (r < m) s[r] = __ldcg(dst + r * SK_BM);
+                }
+            }
+            if (finish && ch < n) {
+                const float sc = __ldg(scales + ch);
+                const float bv = bias ? __ldg(bias + ch) : 0.0f;
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    if (r < m) {
+                        float v = sk_finish(s[r], __ldg(work.unscale + 2 * r),
+                                            __ldg(work.unscale + 2 * r + 1), sc);
+                        if (bias) v = __fadd_rn(v, bv);
+                        y[(size_t)r * ldy + ch] = v;
+                    }
+                }
+            }
+            u = seg_end;
+            ++seg;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                     "r"(SK_TMEM_COLS)
+                     : "memory");
+    }
+}
+
+// Pre-pass.  Blocks 0..15: activation row r of x [m, k] (k % 16 == 0) -> three digit planes at
+// rows r, 16 + r, 32 + r of xd [48, k] and the row's 2^-e as two factors (rows >= m: zeros).
+// Same grid as the streaming GEMV: max|x| * 2^e in [2^19, 2^20).  Blocks >= 16 zero the partial-sum
+// workspace and the arrival counters.
+__global__ void __launch_bounds__(256)
+skinny_prepass_kernel(const float *__restrict__ x, int8_t *__restrict__ xd, float *__restrict__ unscale,
+                      int m, int k, uint4 *__restrict__ zero_base, size_t zero_count) {
+    __shared__ float wmax[8];
+    __shared__ int wbad[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    // x may be the output of the previous kernel in the stream, and the workspace may still be
+    // in use by it: nothing is touched before that kernel has finished.
+    grid_dependency_wait();
+    grid_launch_dependents();
+    if (blockIdx.x >= SK_ROWS) {
+        const size_t nz = gridDim.x - SK_ROWS;
+        for (size_t i = (size_t)(blockIdx.x - SK_ROWS) * 256 + tid; i < zero_count; i += nz * 256)
+            zero_base[i] = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    const int row = blockIdx.x;
+    const int n4 = k >> 2;
+    uint32_t *p0 = reinterpret_cast<uint32_t *>(xd + (size_t)row * k);
+    uint32_t *p1 = reinterpret_cast<uint32_t *>(xd + (size_t)(SK_ROWS + row) * k);
+    uint32_t *p2 = reinterpret_cast<uint32_t *>(xd + (size_t)(2 * SK_ROWS + row) * k);
+    if (row >= m) {
+        for (int i = tid; i < n4; i += 256) p0[i] = p1[i] = p2[i] = 0u;
+        if (tid == 0) unscale[2 * row] = unscale[2 * row + 1] = 0.0f;
+        return;
+    }
+    const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)row * k);
+    // The row is read once: each thread keeps up to 8 float4 of it in registers between the max
+    // pass and the digit pass (k <= 8192); longer rows re-read the rest.
+    float4 keep[8];
+    float mx = 0.0f;
+    int bad = 0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 256;
+        keep[u] = (i < n4) ? __ldg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    auto scan = [&](const float4 &t) {
+        const float a0 = fabsf(t.x), a1 = fabsf(t.y), a2 = fabsf(t.z), a3 = fabsf(t.w);
+        bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) | !(a2 <= 3.402823466e38f) |
+               !(a3 <= 3.402823466e38f);
+        mx = fmaxf(fmaxf(mx, fmaxf(a0, a1)), fmaxf(a2, a3));
+    };
+#pragma unroll
+    for (int u = 0; u < 8; ++u) scan(keep[u]);
+    for (int i = tid + 2048; i < n4; i += 256) scan(__ldg(src + i));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) {
+        wmax[warp] = mx;
+        wbad[warp] = bad;
+    }
+    __syncthreads();
+    mx = 0.0f;
+    bad = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+        mx = fmaxf(mx, wmax[w]);
+        bad |= wbad[w];
+    }
+    const int e = 19 - ((mx > 0.0f) ? ilogbf(mx) : 0);
+    const int e1 = e >> 1, e2 = e - e1;  // 2^e = 2^e1 * 2^e2, both factors finite
+    const float f1 = __int_as_float((127 + e1) << 23), f2 = __int_as_float((127 + e2) << 23);
+    if (tid == 0) {
+        const float nan = __int_as_float(0x7fc00000);
+        unscale[2 * row] = bad ? nan : __int_as_float((127 - e1) << 23);
+        unscale[2 * row + 1] = bad ? nan : __int_as_float((127 - e2) << 23);
+    }
+    auto emit = [&](int i, const float4 &t) {
+        const float xv[4] = {t.x, t.y, t.z, t.w};
+        uint32_t w0 = 0u, w1 = 0u, w2 = 0u;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int v = bad ? 0 : __float2int_rn(xv[b] * f1 * f2);
+            const int d0 = ((v + 64) & 127) - 64;
+            const int v1 = (v - d0) >> 7;
+            const int d1 = ((v1 + 64) & 127) - 64;
+            const int d2 = (v1 - d1) >> 7;
+            w0 |= (uint32_t)(d0 & 0xff) << (8 * b);
+            w1 |= (uint32_t)(d1 & 0xff) << (8 * b);
+            w2 |= (uint32_t)(d2 & 0xff) << (8 * b);
+        }
+        p0[i] = w0;
+        p1[i] = w1;
+        p2[i] = w2;
+    };
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 256;
+        if (i < n4) emit(i, keep[u]);
+    }
+    for (int i = tid + 2048; i < n4; i += 256) emit(i, __ldg(src + i));
+}
+
+}  // namespace
+
+bool skinny_supports(const nne_qlinear *ql, size_t m) {
+    if (!ql || !ql->tmap_wsk) return false;
+    return m >= 3 && m <= (size_t)SK_ROWS;
+}
+
+int skinny_prepare_layer(nne_qlinear *ql) {
+    ql->tmap_wsk = nullptr;
+    if (ql->n == 0 || ql->k == 0 || ql->k % 16 != 0) return NNE_OK;
+    if (ql->n > 0x7fffff00u || ql->k > 0x7fffff00u) return NNE_OK;
+    if ((reinterpret_cast<uintptr_t>(ql->q) & 15u) != 0) return NNE_OK;
+    CUtensorMap *map = new CUtensorMap;
+    int st = tma_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ql->q, ql->k, ql->n, SK_BKB, SK_BM,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != NNE_OK) {
+        delete map;
+        return NNE_OK;  // no tensor maps on this driver: the layer simply does not take this path
+    }
+    ql->tmap_wsk = map;
+    return NNE_OK;
+}
+
+void skinny_release_layer(nne_qlinear *ql) {
+    if (ql->tmap_wsk) delete static_cast<CUtensorMap *>(ql->tmap_wsk);
+    ql->tmap_wsk = nullptr;
+}
+
+int launch_skinny(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy, cudaStream_t s) {
+    nne_ctx *ctx = ql->ctx;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_skinny_i8_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BYTES));
+        attr_set = true;
+    }
+    const size_t k = ql->k, n = ql->n;
+    const size_t tiles = (n + SK_BM - 1) / SK_BM;
+    const size_t num_kb = (k + SK_BKB - 1) / SK_BKB;
+    // stream-ordered workspace: [sums | arrivals] (zeroed by the pre-pass), unscale, digit planes
+    const size_t sums_bytes = tiles * SK_ROWS * SK_BM * sizeof(long long);
+    const size_t arr_bytes = (tiles * 4 * sizeof(int) + 255) & ~(size_t)255;
+    const size_t zero_bytes = sums_bytes + arr_bytes;  // a multiple of 16
+    const size_t uns_bytes = 256;
+    const size_t xd_bytes = (size_t)SK_N * k;
+    uint8_t *ws = nullptr;
+    NNE_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void **>(&ws), zero_bytes + uns_bytes + xd_bytes, s));
+    SkWork work;
+    work.sums = reinterpret_cast<long long *>(ws);
+    work.arrivals = reinterpret_cast<int *>(ws + sums_bytes);
+    float *unscale = reinterpret_cast<float *>(ws + zero_bytes);
+    work.unscale = unscale;
+    int8_t *xd = reinterpret_cast<int8_t *>(ws + zero_bytes + uns_bytes);
+
+    cudaLaunchAttribute pdl[1];
+    pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pdl[0].val.programmaticStreamSerializationAllowed = 1;
+    {
+        size_t zblocks = (zero_bytes / 16 + 2047) / 2048;  // 8 uint4 per thread
+        if (zblocks < 1) zblocks = 1;
+        if (zblocks > 64) zblocks = 64;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(SK_ROWS + zblocks));
+        cfg.blockDim = dim3(256);
+        cfg.stream = s;
+        cfg.attrs = pdl;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_prepass_kernel, x, xd, unscale, (int)m, (int)k,
+                                           reinterpret_cast<uint4 *>(ws), zero_bytes / 16);
+        count_launch();
+        if (e != cudaSuccess) {
+            cudaFreeAsync(ws, s);
+            return fail(NNE_ERR_CUDA, "skinny pre-pass launch failed: %s", cudaGetErrorString(e));
+        }
+    }
+    CUtensorMap tmap_x;
+    int st = tma_make_map_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xd, k, SK_N, SK_BKB, SK_N,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st != NNE_OK) {
+        cudaFreeAsync(ws, s);
+        return st;
+    }
+    const long long total = (long long)tiles * (long long)num_kb;
+    int grid = ctx->sm_count;
+    if (grid > total) grid = (int)total;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3((unsigned)SK_THREADS);
+    cfg.dynamicSmemBytes = SK_SMEM_BYTES;
+    cfg.stream = s;
+    cfg.attrs = pdl;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, qlinear_skinny_i8_kernel,
+                                       *static_cast<const CUtensorMap *>(ql->tmap_wsk), tmap_x, work,
+                                       (const float *)ql->scales, (const float *)ql->bias, y, (int)m,
+                                       (int)n, (int)k, ldy, ctx->err_word);
+    count_launch();
+    cudaFreeAsync(ws, s);
+    if (e != cudaSuccess)
+        return fail(NNE_ERR_CUDA, "skinny kernel launch failed: %s", cudaGetErrorString(e));
+    return NNE_OK;
+}
+
+}  // namespace nne

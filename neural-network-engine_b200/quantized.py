@@ -281,7 +281,8 @@ class QLinear:
             _raise_mapped(e)
 
     def kernel_for(self, m: int) -> int:
-        """1 = streaming GEMV, 2 = tcgen05 tensor-core kernel, 3 = generic kernel."""
+        """1 = streaming GEMV, 2 = tcgen05 tensor-core kernel, 3 = generic kernel,
+        4 = small-batch tcgen05 kernel (3 <= m <= 16)."""
         return int(load().nne_qlinear_kernel_for(self._live_handle(), m))
 
     # -- the rest of the reference surface -----------------------------------------------------
