@@ -11,7 +11,8 @@ weights come from HBM, not L2.  The layers of a step do not depend on each other
 issued as one plan (nne_qlinear_plan_run: one kernel launch that streams all the layers); the
 same step issued as one launch per layer is reported beside it under "per_layer_launches".
 metric = int8-weight streaming rate in GB/s, counting the algorithmic bytes
-N*K + 4N + 4K + 4N per forward.  The same line carries the M=2048 prefill figure (TFLOP/s) under
+N*K + 4N + 4K + 4N per forward.  The same line carries the decode batch sweep (M in 1..16, one
+forward per layer) under "decode_batch_sweep" and the M=2048 prefill figure (TFLOP/s) under
 "prefill".
 
 N > 1 (torchrun, one rank per GPU): every rank holds its own column shard of N-times-wider layers
@@ -38,6 +39,7 @@ sys.path.insert(0, ROOT)
 SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008)]  # (N, K)
 REPLICAS = 4  # copies of each shape in the rotation set: 4 * 107 MB = 428 MB > 126 MB L2
 PREFILL_SHAPES = [(11008, 4096), (4096, 11008)]
+DECODE_SWEEP_M = (1, 2, 4, 8, 16)
 PREFILL_M = 2048
 # dram__bytes_read.sum + dram__bytes_write.sum of one qgemv_stream_kernel launch over the rotation
 # set (read 428.5 MB + write 5.1 MB), from the ncu capture summarised in
@@ -255,6 +257,9 @@ def run_native(args):
         raise RuntimeError(nne._lib.last_error())
     launches_per_step = lib.nne_qlinear_plan_launches(plan)
 
+    # N > 1: the all-gather follows the plan launch on the same stream.  (Issuing it on a second
+    # stream, with two output slabs, was measured and gains nothing: a collective's CTAs do not fit
+    # on an SM beside this kernel's persistent CTA, so it runs between two plan launches anyway.)
     def step():
         if lib.nne_qlinear_plan_run(plan, torch.cuda.current_stream().cuda_stream) != 0:
             raise RuntimeError(nne._lib.last_error())
@@ -360,6 +365,11 @@ def run_native(args):
     h2d = sum(4 * L["k"] for L in layers)
     d2h = sum(4 * L["n"] for L in layers)
 
+    # decode batch sweep (config 2): one forward per layer over the rotation set, M rows each
+    sweep = None
+    if world == 1:
+        sweep = run_decode_sweep(nne, lib, dev, layers)
+
     # prefill (M = 2048) on the tensor-core kernel, when it is built in
     prefill = None
     if world == 1:
@@ -397,6 +407,8 @@ def run_native(args):
         }
         if per_layer is not None:
             out["per_layer_launches"] = per_layer
+        if sweep is not None:
+            out["decode_batch_sweep"] = sweep
         if prefill is not None:
             out["prefill"] = prefill
         print(json.dumps(out))
@@ -405,6 +417,42 @@ def run_native(args):
         lib.nne_qlinear_destroy(L["h"])
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_decode_sweep(nne, lib, dev, layers):
+    """M in {1, 2, 4, 8, 16}: forwards of the 12-layer rotation set issued one layer at a time,
+    back to back on one stream; GB/s = algorithmic bytes / device time."""
+    import torch
+    stream = torch.cuda.current_stream()
+    cases = []
+    for m in DECODE_SWEEP_M:
+        xs = [torch.randn(m, L["k"], device=dev, dtype=torch.float32) for L in layers]
+        ys = [torch.empty(m, L["n"], device=dev, dtype=torch.float32) for L in layers]
+
+        def sweep_step():
+            for L, x, y in zip(layers, xs, ys):
+                if lib.nne_qlinear_forward_dev(L["h"], x.data_ptr(), m, L["k"], y.data_ptr(),
+                                               stream.cuda_stream) != 0:
+                    raise RuntimeError(nne._lib.last_error())
+
+        for _ in range(3):
+            sweep_step()
+        torch.cuda.synchronize()
+        iters = 20
+        l0 = lib.nne_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            sweep_step()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        nbytes = sum(algorithmic_bytes(L["n"], L["k"], m) for L in layers)
+        cases.append({"m": m, "GB/s": nbytes / (ms * 1e-3) / 1e9, "us_per_layer": ms * 1e3 / len(layers),
+                      "kernel": int(lib.nne_qlinear_kernel_for(layers[0]["h"], m)),
+                      "launches_per_layer": (lib.nne_launch_count() - l0) / (iters * len(layers))})
+    return {"cases": cases, "launch": "one forward per layer, back to back (no plan, no graph)",
+            "kernels": {"1": "qgemv_stream_kernel", "4": "qlinear_skinny_i8_kernel"}}
 
 
 def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):
