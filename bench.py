@@ -333,8 +333,33 @@ def run_native(args):
                      "launches_per_step": nl, "avg_launch_us": gms * 1e3 / (args.steps * nl),
                      "launch": "CUDA graph replay of 12 single-layer launches"}
 
-    # end-to-end: the host-pointer entry point (what QLinear::forward calls), pinned host buffers,
-    # H2D of x and D2H of y inside every call.
+    # end-to-end: host buffers in, host buffers out, H2D and D2H inside every timed step.
+    # (1) the step as the plan runs it: nne_qlinear_plan_run_host over one pinned x slab and one
+    #     pinned y slab (one copy each way around the one launch);
+    # (2) layer by layer through nne_qlinear_forward_host (what QLinear::forward binds to).
+    x_total = sum(L["k"] for L in layers)
+    y_total = sum(L["n"] for L in layers)
+    xslab = torch.empty(x_total, device=dev, dtype=torch.float32)
+    yslab = torch.empty(y_total, device=dev, dtype=torch.float32)
+    xh_all = torch.empty(x_total, dtype=torch.float32).pin_memory()
+    yh_all = torch.empty(y_total, dtype=torch.float32).pin_memory()
+    xo = yo = 0
+    xps, yps = [], []
+    for L in layers:
+        xh_all[xo:xo + L["k"]].copy_(L["x"].view(-1).cpu())
+        xps.append(xslab.data_ptr() + 4 * xo)
+        yps.append(yslab.data_ptr() + 4 * yo)
+        xo += L["k"]
+        yo += L["n"]
+    hplan = C.c_void_p()
+    if lib.nne_qlinear_plan_create(ctx.handle, nl, hs, (C.c_void_p * nl)(*xps), (C.c_void_p * nl)(*yps), 1,
+                                   C.byref(hplan)) != 0:
+        raise RuntimeError(nne._lib.last_error())
+
+    def e2e_step():
+        if lib.nne_qlinear_plan_run_host(hplan, xh_all.data_ptr(), yh_all.data_ptr()) != 0:
+            raise RuntimeError(nne._lib.last_error())
+
     host = []
     for L in layers:
         xh = torch.empty(1, L["k"], dtype=torch.float32).pin_memory()
@@ -342,33 +367,44 @@ def run_native(args):
         yh = torch.empty(1, L["n"], dtype=torch.float32).pin_memory()
         host.append((xh, yh))
 
-    def e2e_step():
+    def e2e_layer_step():
         for L, (xh, yh) in zip(layers, host):
             st = lib.nne_qlinear_forward_host(L["h"], xh.data_ptr(), 1, L["k"], yh.data_ptr())
             if st != 0:
                 raise RuntimeError(nne._lib.last_error())
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
+    def time_host(fn, steps):
+        for _ in range(3):
+            fn()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()
+        torch.cuda.synchronize()
+        sec = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([sec], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            sec = float(t.item())
+        return sec
+
     e2e_steps = max(args.steps, 5)
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    e2e_s = time_host(e2e_step, e2e_steps)
+    e2e_layer_s = time_host(e2e_layer_step, min(e2e_steps, 200))
     e2e_value = step_bytes * world * e2e_steps / e2e_s / 1e9
+    e2e_layer_value = step_bytes * world * min(e2e_steps, 200) / e2e_layer_s / 1e9
+    # the two routes must agree bit for bit
+    got = torch.cat([yh.view(-1) for _, yh in host])
+    if not torch.equal(got.view(torch.int32), yh_all.view(torch.int32)):
+        raise RuntimeError("plan and per-layer host results differ")
+    lib.nne_qlinear_plan_destroy(hplan)
     h2d = sum(4 * L["k"] for L in layers)
     d2h = sum(4 * L["n"] for L in layers)
 
     # decode batch sweep (config 2): one forward per layer over the rotation set, M rows each
     sweep = None
     if world == 1:
-        sweep = run_decode_sweep(nne, lib, dev, layers)
+        sweep = run_decode_sweep(nne, lib, dev, layers, args)
 
     # prefill (M = 2048) on the tensor-core kernel, when it is built in
     prefill = None
@@ -401,7 +437,11 @@ def run_native(args):
                              "sample": cpu_sample},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "api": "nne_qlinear_forward_host (pinned host x and y, per call H2D + D2H)"},
+                    "api": "nne_qlinear_plan_run_host (pinned host x and y slabs; H2D, one launch, D2H, "
+                           "sync in every step)",
+                    "per_layer": {"value": e2e_layer_value, "unit": "GB/s",
+                                  "api": "nne_qlinear_forward_host, 12 calls per step (per call H2D + "
+                                         "launch + D2H + sync)"}},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
@@ -419,7 +459,7 @@ def run_native(args):
         dist.destroy_process_group()
 
 
-def run_decode_sweep(nne, lib, dev, layers):
+def run_decode_sweep(nne, lib, dev, layers, args):
     """M in {1, 2, 4, 8, 16}: forwards of the 12-layer rotation set issued one layer at a time,
     back to back on one stream; GB/s = algorithmic bytes / device time."""
     import torch
@@ -438,7 +478,7 @@ def run_decode_sweep(nne, lib, dev, layers):
         for _ in range(3):
             sweep_step()
         torch.cuda.synchronize()
-        iters = 20
+        iters = 20 if args.steps >= 20 else max(3, args.steps)
         l0 = lib.nne_launch_count()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
@@ -479,7 +519,7 @@ def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):
         for _ in range(3):
             fwd()
         torch.cuda.synchronize()
-        iters = 20
+        iters = 20 if args.steps >= 20 else max(3, args.steps)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
         for _ in range(iters):

@@ -177,8 +177,18 @@ NNE_API int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *con
                                     const float *const *x_dev, float *const *y_dev, size_t m,
                                     nne_plan **out);
 NNE_API int nne_qlinear_plan_run(nne_plan *plan, void *stream);
+/* The same run with HOST activations and outputs: x_all_host holds the x_i one after another
+ * (m * k_i floats each, list order), y_all_host receives the y_i one after another (m * n_i
+ * floats each).  Copies them to and from the plan's device buffers (one copy per run of buffers
+ * that continue one another in device memory, so a plan built over one x slab and one y slab
+ * costs one copy each way), runs the plan on the context's stream and returns when y_all_host is
+ * complete.  Serialised per context like the other *_host entry points.  The reference has no
+ * counterpart; it is what a caller of QLinear::forward on several independent projections
+ * (q/k/v: src/models/llama.rs:226-228) gets instead of one host round trip per projection. */
+NNE_API int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_all_host);
 NNE_API int nne_qlinear_plan_destroy(nne_plan *plan);
-/* Number of kernel launches one run of the plan makes. */
+/* 1 when the whole list runs as one streaming launch, else the number of layers (each then runs
+ * its own forward, of one or two launches). */
 NNE_API int nne_qlinear_plan_launches(const nne_plan *plan);
 
 /* Which kernel a forward of m rows on this layer dispatches to: 1 = streaming GEMV (small m),

@@ -64,6 +64,7 @@ SIGNATURES = {
     "nne_qlinear_plan_create": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp, c_void_pp, c_void_pp,
                                           C.c_size_t, c_void_pp]),
     "nne_qlinear_plan_run": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "nne_qlinear_plan_run_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "nne_qlinear_plan_destroy": (C.c_int, [C.c_void_p]),
     "nne_qlinear_plan_launches": (C.c_int, [C.c_void_p]),
     "nne_qlinear_kernel_for": (C.c_int, [C.c_void_p, C.c_size_t]),

@@ -677,6 +677,59 @@ int nne_qlinear_plan_run(nne_plan *plan, void *stream) {
     NNE_GUARD_END
 }
 
+int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_all_host) {
+    NNE_GUARD_BEGIN
+    if (!plan || !plan->ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null plan");
+    if (plan->layers.empty() || plan->m == 0) return NNE_OK;
+    if (!x_all_host || !y_all_host) return fail(NNE_ERR_INVALID_ARGUMENT, "null host pointer");
+    nne_ctx *ctx = plan->ctx;
+    NNE_TRY(use_ctx(ctx));
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaStream_t s = ctx->stream;
+    const size_t count = plan->layers.size();
+    // Neighbouring device buffers that continue one another are moved with one copy.
+    size_t i = 0, off = 0;
+    while (i < count) {
+        size_t j = i, len = 0;
+        const float *base = plan->x[i];
+        while (j < count && plan->x[j] == base + len) len += plan->m * plan->layers[j++]->k;
+        if (len)
+            NNE_CUDA_TRY(cudaMemcpyAsync(const_cast<float *>(base), x_all_host + off, len * sizeof(float),
+                                         cudaMemcpyHostToDevice, s));
+        off += len;
+        i = j;
+    }
+    if (plan->fused) {
+        NNE_TRY(launch_stream_batch(ctx, plan->descs.data(), plan->descs_dev, (int)plan->descs.size(),
+                                    plan->m, false, s));
+    } else {
+        for (size_t l = 0; l < count; ++l)
+            NNE_TRY(forward_dev(plan->layers[l], plan->x[l], plan->m, plan->layers[l]->k, plan->y[l],
+                                plan->layers[l]->n, s));
+    }
+    i = 0;
+    off = 0;
+    while (i < count) {
+        size_t j = i, len = 0;
+        float *base = plan->y[i];
+        while (j < count && plan->y[j] == base + len) len += plan->m * plan->layers[j++]->n;
+        if (len)
+            NNE_CUDA_TRY(cudaMemcpyAsync(y_all_host + off, base, len * sizeof(float),
+                                         cudaMemcpyDeviceToHost, s));
+        off += len;
+        i = j;
+    }
+    int word = 0;
+    NNE_CUDA_TRY(cudaMemcpyAsync(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost, s));
+    NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    if (word != 0) {
+        cudaMemsetAsync(ctx->err_word, 0, sizeof(int), s);
+        return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
+    }
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
 int nne_qlinear_plan_launches(const nne_plan *plan) {
     if (!plan) return 0;
     return plan->fused ? 1 : (int)plan->layers.size();

@@ -335,6 +335,7 @@ class QLinearPlan:
         except NneError as e:
             _raise_mapped(e)
         self._h, self._layers, self._ctx = h, list(layers), ctx  # keep the layers alive
+        self._m = int(m)
 
     @property
     def launches(self) -> int:
@@ -345,6 +346,25 @@ class QLinearPlan:
             check(load().nne_qlinear_plan_run(self._h, stream))
         except NneError as e:
             _raise_mapped(e)
+
+    def run_host(self, x_all: np.ndarray, y_all: Optional[np.ndarray] = None) -> np.ndarray:
+        """Host round trip of the whole plan: ``x_all`` holds the activations of all layers one
+        after another (f32), the outputs come back the same way."""
+        m = self._m
+        nx = sum(m * l.in_features for l in self._layers)
+        ny = sum(m * l.out_features for l in self._layers)
+        x_all = np.ascontiguousarray(x_all, dtype=np.float32).reshape(-1)
+        if x_all.size != nx:
+            raise ShapeMismatch([nx], [x_all.size])
+        if y_all is None:
+            y_all = np.empty(ny, dtype=np.float32)
+        if y_all.size != ny or y_all.dtype != np.float32 or not y_all.flags.c_contiguous:
+            raise InvalidArgument("y_all must be a contiguous f32 array of the plan's output size")
+        try:
+            check(load().nne_qlinear_plan_run_host(self._h, _ptr(x_all), _ptr(y_all)))
+        except NneError as e:
+            _raise_mapped(e)
+        return y_all
 
     def close(self):
         if getattr(self, "_h", None) is not None:

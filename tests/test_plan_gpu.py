@@ -68,3 +68,37 @@ def test_plan_argument_errors(nne, ctx):
         nne.QLinearPlan(layers, [0], [ys[0].data_ptr()], 1, ctx)
     empty = nne.QLinearPlan(layers, [xs[0].data_ptr()], [ys[0].data_ptr()], 0, ctx)
     empty.run(0)  # m = 0: nothing to do
+
+
+@pytest.mark.parametrize("m,slabs", [(1, True), (2, False), (5, True)])
+def test_plan_run_host_equals_single_forwards(nne, ctx, m, slabs):
+    """Host round trip of a plan: one slab each way (buffers continue one another) or one copy
+    per layer (scattered buffers); m = 5 takes the layer-by-layer path."""
+    import torch
+    shapes = [(300, 512, True), (129, 4096, False), (64, 1024, True), (256, 256, False)]
+    layers, xs, ys, refs = build(nne, ctx, shapes, m, 97 + m)
+    if slabs:
+        xslab = torch.empty(sum(m * k for _, k, _ in shapes), device="cuda")
+        yslab = torch.full((sum(m * n for n, _, _ in shapes),), float("nan"), device="cuda")
+        xp, yp, xo, yo = [], [], 0, 0
+        for n, k, _ in shapes:
+            xp.append(xslab.data_ptr() + 4 * xo)
+            yp.append(yslab.data_ptr() + 4 * yo)
+            xo += m * k
+            yo += m * n
+    else:
+        xp, yp = [t.data_ptr() for t in xs], [t.data_ptr() for t in ys]
+    plan = nne.QLinearPlan(layers, xp, yp, m, ctx)
+    x_all = np.concatenate([x.reshape(-1) for (_, x, _) in refs])
+    y_all = plan.run_host(x_all)
+    y_again = plan.run_host(x_all)
+    ctx.check()
+    assert np.array_equal(y_all.view(np.uint32), y_again.view(np.uint32))
+    off = 0
+    for (ql, x, b) in refs:
+        single = ql.forward(x).reshape(-1)
+        got = y_all[off:off + single.size]
+        assert np.array_equal(got.view(np.uint32), single.view(np.uint32))
+        off += single.size
+    with pytest.raises(nne.ShapeMismatch):
+        plan.run_host(x_all[:-1])
