@@ -1,0 +1,109 @@
+"""Config 4 of the benchmark plan: a LLaMA-2-7B-shaped decoder stack of QLinears (32 layers of
+q/k/v/o 4096->4096, gate/up 4096->11008, down 11008->4096; 224 layers, 6.5 GB of int8 codes), one
+decode step at batch 1 and batch 8, each layer fed by the one before it.
+
+The weights are drawn on the device (the CPU generator would need minutes for 6.5 G values), so
+parity is checked two ways that do not need them on the host:
+  * against the oracle on SAMPLED layers (first and last), with the codes downloaded through the C
+    ABI and the layer's actual device input copied back;
+  * through a size-independent property over the whole 224-layer chain: row r of the batch-8 step
+    (small-batch tensor-core kernel) equals, bit for bit, the batch-1 step of that row alone
+    (streaming GEMV) - any error in either kernel is amplified by the 32 layers behind it."""
+import ctypes as C
+import time
+
+import numpy as np
+import pytest
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+H, F, LAYERS = 4096, 11008, 32
+NAMES = [("q", H, H), ("k", H, H), ("v", H, H), ("o", H, H), ("gate", F, H), ("up", F, H), ("down", H, F)]
+
+
+def test_config4_decoder_stack(nne, ctx):
+    import torch
+    lib = nne.load()
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(4)
+    stream = torch.cuda.current_stream().cuda_stream
+    stack = []
+    for _ in range(LAYERS):
+        layer = {}
+        for name, n, k in NAMES:
+            w = torch.randn(n, k, generator=gen, device=dev) * 0.02
+            h = C.c_void_p()
+            assert lib.nne_qlinear_create_from_f32_dev(ctx.handle, w.data_ptr(), None, n, k, stream,
+                                                       C.byref(h)) == 0
+            layer[name] = h
+            del w
+        stack.append(layer)
+    torch.cuda.synchronize()
+    total_bytes = sum(lib.nne_qlinear_memory_bytes(h) for layer in stack for h in layer.values())
+    assert total_bytes == LAYERS * (4 * (H * H + 4 * H) + 3 * (H * F) + 2 * 4 * F + 4 * H)
+
+    def fwd(h, x, m, k, y):
+        assert lib.nne_qlinear_forward_dev(h, x.data_ptr(), m, k, y.data_ptr(), stream) == 0
+
+    def decode_step(x0, keep=None):
+        """x0 [b, H] on the device -> hidden state after 32 layers; `keep` collects (input, output)
+        of sampled projections."""
+        b = x0.shape[0]
+        hcur = x0.clone()
+        q, kk, v, o, d = (torch.empty(b, H, device=dev) for _ in range(5))
+        g, u = (torch.empty(b, F, device=dev) for _ in range(2))
+        for li, layer in enumerate(stack):
+            fwd(layer["q"], hcur, b, H, q)
+            fwd(layer["k"], hcur, b, H, kk)
+            fwd(layer["v"], hcur, b, H, v)
+            fwd(layer["o"], q, b, H, o)          # q stands in for the attention output
+            fwd(layer["gate"], o, b, H, g)
+            fwd(layer["up"], o, b, H, u)
+            fwd(layer["down"], g, b, F, d)
+            if keep is not None and li in (0, LAYERS - 1):
+                keep[(li, "q")] = (hcur.cpu().numpy().copy(), q.cpu().numpy().copy())
+                keep[(li, "down")] = (g.cpu().numpy().copy(), d.cpu().numpy().copy())
+            hcur, d = d, hcur
+        torch.cuda.synchronize()
+        return hcur
+
+    x8 = torch.randn(8, H, generator=gen, device=dev)
+    keep = {}
+    out8 = decode_step(x8, keep)
+    ctx.check()
+    assert bool(torch.isfinite(out8).all())
+
+    # (1) sampled layers against the oracle
+    for (li, name), (xin, yout) in keep.items():
+        n, k = (H, H) if name == "q" else (H, F)
+        qw = np.empty((n, k), dtype=np.int8)
+        sc = np.empty(n, dtype=np.float32)
+        assert lib.nne_qlinear_download(stack[li][name], qw.ctypes.data_as(C.c_void_p),
+                                        sc.ctypes.data_as(C.c_void_p)) == 0
+        y_ref = oracle.forward(qw, sc, None, xin)
+        tol, _ = oracle.tolerance(qw, sc, xin)
+        ratio = float((np.abs(yout - y_ref) / tol).max())
+        print(f"config4 layer {li} {name}: max err/tol {ratio:.3e}")
+        assert ratio <= 1.0
+
+    # (2) batch invariance over the whole chain: different kernels, identical bits
+    for r in (0, 5):
+        out1 = decode_step(x8[r:r + 1].contiguous())
+        assert torch.equal(out1.view(torch.int32)[0], out8.view(torch.int32)[r]), f"row {r} differs"
+    ctx.check()
+
+    # informational: linear-layer time of one decode step (224 dependent forwards, issued eagerly)
+    for b in (1, 8):
+        xb = x8[:b].contiguous()
+        decode_step(xb)
+        t0 = time.perf_counter()
+        decode_step(xb)
+        dt = time.perf_counter() - t0
+        print(f"config4 batch {b}: {dt * 1e3:.2f} ms per decode step of the linear layers, "
+              f"{b / dt:.0f} tokens/s, {total_bytes / dt / 1e9:.0f} GB/s of weights")
+    for layer in stack:
+        for h in layer.values():
+            lib.nne_qlinear_destroy(h)
