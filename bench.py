@@ -40,6 +40,7 @@ SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008)]  # (N, K)
 REPLICAS = 4  # copies of each shape in the rotation set: 4 * 107 MB = 428 MB > 126 MB L2
 PREFILL_SHAPES = [(11008, 4096), (4096, 11008)]
 DECODE_SWEEP_M = (1, 2, 4, 8, 16)
+RESERVED_SMS = 4  # N > 1: SMs left to the all-gather that runs beside the next step's kernel
 PREFILL_M = 2048
 # dram__bytes_read.sum + dram__bytes_write.sum of one qgemv_stream_kernel launch over the rotation
 # set (read 428.5 MB + write 5.1 MB), from the ncu capture summarised in
@@ -209,6 +210,7 @@ def run_native(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_MAX_CTAS", str(RESERVED_SMS))
         dist.init_process_group("nccl", device_id=dev)
 
     nne = importlib.import_module("neural-network-engine_b200")
@@ -231,40 +233,68 @@ def run_native(args):
 
     # rotation set: REPLICAS independently drawn copies of each shape (this rank's shard when N>1).
     # Outputs of all layers live in one slab per rank, so that N > 1 gathers a step's output
-    # slices with a single NCCL all-gather.
+    # slices with a single NCCL all-gather.  N > 1 alternates two slabs: the gather of step i runs
+    # on a second stream beside the kernel of step i+1, which writes the other slab.
     specs = [(n, k) for _ in range(REPLICAS) for (n, k) in SHAPES]
     slab_len = sum(n for n, _ in specs)
-    gathered = torch.zeros(world, slab_len, device=dev, dtype=torch.float32)
-    own = gathered[rank]
+    overlap = world > 1 and os.environ.get("NNE_BENCH_OVERLAP", "1") != "0"
+    nslabs = 2 if overlap else 1
+    gathered = [torch.zeros(world, slab_len, device=dev, dtype=torch.float32) for _ in range(nslabs)]
+    own = [g[rank] for g in gathered]
     layers, off = [], 0
     for i, (n, k) in enumerate(specs):
         h = make_layer(n, k, 2 + 1000 * rank + i)
         g = torch.Generator(device=dev)
         g.manual_seed(100 + i)  # activations are replicated: the same on every rank
         x = torch.randn(1, k, generator=g, device=dev, dtype=torch.float32)
-        layers.append({"h": h, "n": n, "k": k, "x": x, "y_own": own[off:off + n]})
+        layers.append({"h": h, "n": n, "k": k, "x": x, "off": off, "y_own": own[0][off:off + n]})
         off += n
     step_bytes = sum(algorithmic_bytes(L["n"], L["k"], 1) for L in layers)
     stream = torch.cuda.current_stream()
 
-    # The step as ONE launch: a plan over the whole rotation set (nne_qlinear_plan_*).
+    # The step as ONE launch: a plan over the whole rotation set (nne_qlinear_plan_*), one plan
+    # per output slab.
     nl = len(layers)
     hs = (C.c_void_p * nl)(*[L["h"] for L in layers])
     xs = (C.c_void_p * nl)(*[L["x"].data_ptr() for L in layers])
-    ys = (C.c_void_p * nl)(*[L["y_own"].data_ptr() for L in layers])
-    plan = C.c_void_p()
-    if lib.nne_qlinear_plan_create(ctx.handle, nl, hs, xs, ys, 1, C.byref(plan)) != 0:
-        raise RuntimeError(nne._lib.last_error())
-    launches_per_step = lib.nne_qlinear_plan_launches(plan)
-
-    # N > 1: the all-gather follows the plan launch on the same stream.  (Issuing it on a second
-    # stream, with two output slabs, was measured and gains nothing: a collective's CTAs do not fit
-    # on an SM beside this kernel's persistent CTA, so it runs between two plan launches anyway.)
-    def step():
-        if lib.nne_qlinear_plan_run(plan, torch.cuda.current_stream().cuda_stream) != 0:
+    plans = []
+    for sl in range(nslabs):
+        ys = (C.c_void_p * nl)(*[own[sl][L["off"]:L["off"] + L["n"]].data_ptr() for L in layers])
+        p = C.c_void_p()
+        if lib.nne_qlinear_plan_create(ctx.handle, nl, hs, xs, ys, 1, C.byref(p)) != 0:
             raise RuntimeError(nne._lib.last_error())
-        if world > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), own)
+        plans.append(p)
+    launches_per_step = lib.nne_qlinear_plan_launches(plans[0])
+    if overlap:
+        # The persistent streaming kernel leaves a few SMs to the collective's CTAs (their number
+        # is capped through NCCL_MAX_CTAS before the process group is created).
+        if lib.nne_cuda_ctx_reserve_sms(ctx.handle, RESERVED_SMS) != 0:
+            raise RuntimeError(nne._lib.last_error())
+    comm = torch.cuda.Stream() if overlap else None
+    plan_done = [torch.cuda.Event() for _ in range(nslabs)]
+    gather_done = [torch.cuda.Event() for _ in range(nslabs)]
+    step_no = [0]
+
+    def step():
+        sl = step_no[0] % nslabs
+        if overlap and step_no[0] >= nslabs:
+            stream.wait_event(gather_done[sl])  # the gather that last read this slab is over
+        step_no[0] += 1
+        if lib.nne_qlinear_plan_run(plans[sl], stream.cuda_stream) != 0:
+            raise RuntimeError(nne._lib.last_error())
+        if overlap:
+            plan_done[sl].record(stream)
+            with torch.cuda.stream(comm):
+                comm.wait_event(plan_done[sl])
+                dist.all_gather_into_tensor(gathered[sl].view(-1), own[sl])
+                gather_done[sl].record(comm)
+        elif world > 1:
+            dist.all_gather_into_tensor(gathered[0].view(-1), own[0])
+
+    def drain():
+        if overlap:
+            for sl in range(min(nslabs, step_no[0])):
+                stream.wait_event(gather_done[sl])
 
     def per_layer_step():
         s = torch.cuda.current_stream().cuda_stream
@@ -280,6 +310,7 @@ def run_native(args):
 
     for _ in range(max(args.warmup, 3)):
         step()
+    drain()
     barrier()
 
     # device-timed region: K steps back to back on one stream
@@ -293,6 +324,7 @@ def run_native(args):
     e0.record(stream)
     for _ in range(args.steps):
         step()
+    drain()
     e1.record(stream)
     barrier()
     launches = lib.nne_launch_count() - launches0
@@ -425,7 +457,9 @@ def run_native(args):
                        "l2": "rotation set of distinct weights larger than the 126 MB L2",
                        "launch": "one plan launch per step (nne_qlinear_plan_run), steps back to back",
                        "parallelism": "1 GPU" if world == 1 else
-                       f"column shards over {world} GPUs + one NCCL all-gather of the step's output slices"},
+                       f"column shards over {world} GPUs + one NCCL all-gather of the step's output slices"
+                       + (f", on a second stream beside the next step's kernel ({RESERVED_SMS} SMs left free for it)"
+                          if overlap else "")},
             "roofline": {"bound": "hbm", "kernel": "qgemv_stream_kernel", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
@@ -452,7 +486,8 @@ def run_native(args):
         if prefill is not None:
             out["prefill"] = prefill
         print(json.dumps(out))
-    lib.nne_qlinear_plan_destroy(plan)
+    for p in plans:
+        lib.nne_qlinear_plan_destroy(p)
     for L in layers:
         lib.nne_qlinear_destroy(L["h"])
     if world > 1:

@@ -73,6 +73,11 @@ NNE_API int nne_cuda_ctx_destroy(nne_ctx *ctx);
  * NNE_ERR_TIMEOUT (and clears the word) if that happened since the last check, else NNE_OK.  The
  * `_host` entry points perform this check themselves. */
 NNE_API int nne_cuda_ctx_check(nne_ctx *ctx);
+/* The streaming GEMV (m <= 2, and every plan it runs) is a persistent kernel with one CTA per SM;
+ * a kernel of another library launched beside it (an NCCL collective on a second stream) finds no
+ * SM with room for its CTAs and waits for it to end.  This leaves `count` SMs out of that kernel's
+ * grid, so that the two overlap.  0 (the default) uses every SM.  No counterpart in the reference. */
+NNE_API int nne_cuda_ctx_reserve_sms(nne_ctx *ctx, int count);
 /* Device facts the host side sizes its work with.  Any out pointer may be NULL. */
 NNE_API int nne_cuda_ctx_info(const nne_ctx *ctx, int *device, int *sm_count, int *cc_major,
                               int *cc_minor, size_t *total_mem_bytes);

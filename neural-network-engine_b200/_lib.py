@@ -63,6 +63,7 @@ SIGNATURES = {
                                                  C.c_void_p, C.c_void_p]),
     "nne_qlinear_plan_create": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp, c_void_pp, c_void_pp,
                                           C.c_size_t, c_void_pp]),
+    "nne_cuda_ctx_reserve_sms": (C.c_int, [C.c_void_p, C.c_int]),
     "nne_qlinear_plan_run": (C.c_int, [C.c_void_p, C.c_void_p]),
     "nne_qlinear_plan_run_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "nne_qlinear_plan_destroy": (C.c_int, [C.c_void_p]),

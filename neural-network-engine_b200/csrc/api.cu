@@ -259,6 +259,16 @@ int nne_cuda_ctx_check(nne_ctx *ctx) {
     NNE_GUARD_END
 }
 
+int nne_cuda_ctx_reserve_sms(nne_ctx *ctx, int count) {
+    NNE_GUARD_BEGIN
+    if (!ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null context");
+    if (count < 0 || count >= ctx->sm_count)
+        return fail(NNE_ERR_INVALID_ARGUMENT, "reserved SM count %d outside [0, %d)", count, ctx->sm_count);
+    ctx->reserved_sms = count;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
 int nne_cuda_ctx_info(const nne_ctx *ctx, int *device, int *sm_count, int *cc_major, int *cc_minor,
                       size_t *total_mem_bytes) {
     if (!ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null context");

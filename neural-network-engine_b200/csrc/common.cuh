@@ -86,6 +86,7 @@ struct GrowBuf {
 struct nne_ctx {
     int device = 0;
     int sm_count = 0;
+    int reserved_sms = 0;  // SMs the persistent streaming kernel leaves free (nne_cuda_ctx_reserve_sms)
     int cc_major = 0, cc_minor = 0;
     size_t total_mem = 0;
     size_t smem_optin = 0;

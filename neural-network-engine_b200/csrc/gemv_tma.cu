@@ -538,7 +538,8 @@ int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer
     const int kpad = (int)(((kmax >> 4) + 31) & ~(size_t)31);
     // a slot holds a stage plus slack for the padded chunk loop of its last row
     const int slot_bytes = (int)((slot_payload + 512 + 127) & ~(size_t)127);
-    int grid = ctx->sm_count;  // all CTAs resident at once: one wave, equal row ranges
+    int grid = ctx->sm_count - ctx->reserved_sms;  // all CTAs resident at once: one wave, equal row ranges
+    if (grid < 1) grid = 1;
     if ((size_t)grid > nmin) grid = (int)nmin;
     int sb_rows = (int)((nmax + grid - 1) / grid) + 1;
     if (sb_rows > 4 * PREP_THREADS) sb_rows = 0;  // the prep warps stage at most 4 rows per thread
