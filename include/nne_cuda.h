@@ -176,8 +176,11 @@ NNE_API int nne_qlinear_forward_dev_static(nne_qlinear *ql, const float *x_dev, 
  * (src/models/llama.rs:344-346), or the per-layer timing loop of the decode benchmark - each
  * of which is the contraction of src/nn/quantized.rs:164-193.  For m <= 2 and streaming-capable
  * shapes the whole list is ONE kernel launch whose weight stream never drains between layers;
- * otherwise the plan runs its layers one after the other.  Results are identical to `count`
- * calls of nne_qlinear_forward_dev.  Layers must outlive the plan.                              */
+ * for 3 <= m <= 16 it is one pre-pass and one launch of the small-batch tensor-core kernel over
+ * all layers (layers given the same x pointer share one set of digit planes; the work areas are
+ * allocated at creation, so a run allocates nothing; a plan must not run concurrently with
+ * itself); otherwise the plan runs its layers one after the other.  Results are identical to
+ * `count` calls of nne_qlinear_forward_dev.  Layers must outlive the plan.                      */
 NNE_API int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *layers,
                                     const float *const *x_dev, float *const *y_dev, size_t m,
                                     nne_plan **out);
@@ -192,8 +195,8 @@ NNE_API int nne_qlinear_plan_run(nne_plan *plan, void *stream);
  * (q/k/v: src/models/llama.rs:226-228) gets instead of one host round trip per projection. */
 NNE_API int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_all_host);
 NNE_API int nne_qlinear_plan_destroy(nne_plan *plan);
-/* 1 when the whole list runs as one streaming launch, else the number of layers (each then runs
- * its own forward, of one or two launches). */
+/* 1 when the whole list runs as one streaming launch, 2 when it runs as pre-pass + small-batch
+ * kernel, else the number of layers (each then runs its own forward, of one or two launches). */
 NNE_API int nne_qlinear_plan_launches(const nne_plan *plan);
 
 /* Which kernel a forward of m rows on this layer dispatches to: 1 = streaming GEMV (small m),

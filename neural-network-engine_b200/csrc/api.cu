@@ -657,12 +657,17 @@ int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *laye
                 gemv_tma_supports(ql->n, ql->k, m);
     }
     plan->fused = fused && count > 0;
+    if (!plan->fused && m >= 3 && !skinny_disabled() &&
+        skinny_plan_supports(layers, x_dev, y_dev, count, m)) {
+        NNE_TRY(skinny_plan_create(ctx, layers, x_dev, y_dev, count, m, &plan->skinny));
+    }
     if (plan->fused && count > (size_t)STREAM_INLINE_LAYERS) {
         NNE_CUDA_TRY(cudaMalloc(&plan->descs_dev, count * sizeof(StreamLayer)));
         cudaError_t e = cudaMemcpy(plan->descs_dev, plan->descs.data(), count * sizeof(StreamLayer),
                                    cudaMemcpyHostToDevice);
         if (e != cudaSuccess) {
             cudaFree(plan->descs_dev);
+            skinny_plan_destroy(plan->skinny);
             return fail(NNE_ERR_CUDA, "plan upload failed: %s", cudaGetErrorString(e));
         }
     }
@@ -680,6 +685,7 @@ int nne_qlinear_plan_run(nne_plan *plan, void *stream) {
     if (plan->fused)
         return launch_stream_batch(plan->ctx, plan->descs.data(), plan->descs_dev,
                                    (int)plan->descs.size(), plan->m, false, s);
+    if (plan->skinny) return skinny_plan_run(plan->skinny, s);
     for (size_t i = 0; i < plan->layers.size(); ++i)
         NNE_TRY(forward_dev(plan->layers[i], plan->x[i], plan->m, plan->layers[i]->k, plan->y[i],
                             plan->layers[i]->n, s));
@@ -712,6 +718,8 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
     if (plan->fused) {
         NNE_TRY(launch_stream_batch(ctx, plan->descs.data(), plan->descs_dev, (int)plan->descs.size(),
                                     plan->m, false, s));
+    } else if (plan->skinny) {
+        NNE_TRY(skinny_plan_run(plan->skinny, s));
     } else {
         for (size_t l = 0; l < count; ++l)
             NNE_TRY(forward_dev(plan->layers[l], plan->x[l], plan->m, plan->layers[l]->k, plan->y[l],
@@ -742,7 +750,9 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
 
 int nne_qlinear_plan_launches(const nne_plan *plan) {
     if (!plan) return 0;
-    return plan->fused ? 1 : (int)plan->layers.size();
+    if (plan->fused) return 1;
+    if (plan->skinny) return 2;  // pre-pass + kernel
+    return (int)plan->layers.size();
 }
 
 int nne_qlinear_plan_destroy(nne_plan *plan) {
@@ -750,6 +760,7 @@ int nne_qlinear_plan_destroy(nne_plan *plan) {
     if (!plan) return NNE_OK;
     if (plan->ctx) cudaSetDevice(plan->ctx->device);
     if (plan->descs_dev) cudaFree(plan->descs_dev);
+    skinny_plan_destroy(plan->skinny);
     delete plan;
     return NNE_OK;
     NNE_GUARD_END

@@ -172,6 +172,13 @@ bool skinny_supports(const nne_qlinear *ql, size_t m);
 int skinny_prepare_layer(nne_qlinear *ql);
 void skinny_release_layer(nne_qlinear *ql);
 int launch_skinny(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy, cudaStream_t s);
+struct SkPlan;  // several small-batch forwards as one launch (skinny.cu)
+bool skinny_plan_supports(nne_qlinear *const *layers, const float *const *x, float *const *y,
+                          size_t count, size_t m);
+int skinny_plan_create(nne_ctx *ctx, nne_qlinear *const *layers, const float *const *x, float *const *y,
+                       size_t count, size_t m, SkPlan **out);
+int skinny_plan_run(SkPlan *plan, cudaStream_t s);
+void skinny_plan_destroy(SkPlan *plan);
 bool prefill_i8_supports(const nne_qlinear *ql, size_t m);
 int prefill_i8_prepare_layer(nne_qlinear *ql);
 void prefill_i8_release_layer(nne_qlinear *ql);
@@ -191,4 +198,5 @@ struct nne_plan {
     std::vector<float *> y;
     std::vector<nne::StreamLayer> descs;
     nne::StreamLayer *descs_dev = nullptr;
+    nne::SkPlan *skinny = nullptr;  // 3 <= m <= 16: the whole list as one small-batch launch
 };

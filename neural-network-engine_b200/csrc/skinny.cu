@@ -25,6 +25,9 @@
 // The pre-pass kernel (digits of x, per-row 2^-e, zeroing of the workspace) runs just before and
 // the two are chained with programmatic dependent launch: the weight ring fills while the
 // pre-pass runs.
+#include <memory>
+#include <vector>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -103,10 +106,27 @@ __host__ __device__ inline int sk_cta_of(long long total, int g, long long u) {
     return (int)(rem + (u - split) / base);
 }
 
-struct SkWork {
-    long long *sums;     // [tiles][16][128] exact partial sums, zeroed by the pre-pass
-    int *arrivals;       // [tiles][4] partial sums delivered so far per lane quarter, zeroed by the pre-pass
+// One layer of a launch.  A single forward passes one of these in the kernel's parameter block; a
+// plan keeps an array of them in device memory (written by the host before any launch).
+struct alignas(64) SkLayer {
+    CUtensorMap tmap_w;    // q [n][k] int8, boxes of 128 rows x 128 bytes
+    CUtensorMap tmap_x;    // digit planes [48][k] of this layer's activations
+    const float *scales;
+    const float *bias;
+    float *y;
+    size_t ldy;
+    long long *sums;       // [tiles][16][128] exact partial sums, zeroed by the pre-pass
+    int *arrivals;         // [tiles][4] partial sums delivered so far per lane quarter, zeroed too
     const float *unscale;  // [16][2]: 2^-e of each row as two factors (NaN for a row with Inf/NaN)
+    long long unit0;       // index of this layer's first (tile, k-block) unit in the launch
+    int n, k, num_kb, tiles;
+};
+// One distinct activation matrix of a launch (layers that read the same x share it).
+struct SkInput {
+    const float *x;
+    int8_t *xd;      // [48][k]
+    float *unscale;  // [16][2]
+    int k;
 };
 
 __device__ __forceinline__ float sk_finish(long long s, float u0, float u1, float scale) {
@@ -114,19 +134,21 @@ __device__ __forceinline__ float sk_finish(long long s, float u0, float u1, floa
     return __fmul_rn(dot, scale);
 }
 
+// Layer that holds unit u, searching forward from li (units are visited in increasing order).
+__device__ __forceinline__ int sk_seek(const SkLayer *layers, int count, long long u, int li) {
+    while (li + 1 < count && u >= layers[li + 1].unit0) ++li;
+    return li;
+}
+
 __global__ void __launch_bounds__(SK_THREADS, 1)
-qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
-                         const __grid_constant__ CUtensorMap tmap_x, SkWork work,
-                         const float *__restrict__ scales, const float *__restrict__ bias,
-                         float *__restrict__ y, int m, int n, int k, size_t ldy, int *err) {
+qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__restrict__ many,
+                         int count, int m, long long total, int *err) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     SkBars *bars = reinterpret_cast<SkBars *>(smem + SK_STAGES * SK_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_kb = (k + SK_BKB - 1) / SK_BKB;
-    const int tiles = (n + SK_BM - 1) / SK_BM;
-    const long long total = (long long)tiles * num_kb;
+    const SkLayer *layers = many ? many : &one;
     long long u0, u1;
     sk_range(total, (int)blockIdx.x, (int)gridDim.x, u0, u1);
     volatile int *abort_flag = &bars->abort_flag;
@@ -162,21 +184,28 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
             // Weights never change after the layer is created: the ring's first round of weight
             // tiles is requested before waiting for the pre-pass that writes the digit planes.
-            int pre = 0;
+            int pre = 0, li = sk_seek(layers, count, u0, 0);
             for (; pre < SK_STAGES && u0 + pre < u1; ++pre) {
                 const long long u = u0 + pre;
-                const int tile = (int)(u / num_kb), kb = (int)(u % num_kb);
+                li = sk_seek(layers, count, u, li);
+                const SkLayer &L = layers[li];
+                const long long lu = u - L.unit0;
+                const int tile = (int)(lu / L.num_kb), kb = (int)(lu % L.num_kb);
                 const uint32_t full = smem_u32(&bars->full[pre]);
                 mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
-                tma_load_2d_hint(smem_u32(smem + pre * SK_STAGE_BYTES), &tmap_w, kb * SK_BKB,
+                tma_load_2d_hint(smem_u32(smem + pre * SK_STAGE_BYTES), &L.tmap_w, kb * SK_BKB,
                                  tile * SK_BM, full, pol_w);
             }
             grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
+            li = sk_seek(layers, count, u0, 0);
             for (long long u = u0; u < u1; ++u) {
-                const int tile = (int)(u / num_kb), kb = (int)(u % num_kb);
+                li = sk_seek(layers, count, u, li);
+                const SkLayer &L = layers[li];
+                const long long lu = u - L.unit0;
+                const int tile = (int)(lu / L.num_kb), kb = (int)(lu % L.num_kb);
                 uint8_t *st = smem + stage * SK_STAGE_BYTES;
                 const uint32_t full = smem_u32(&bars->full[stage]);
                 if (pre > 0) {
@@ -185,9 +214,9 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, err, 0x31);
                     if (!ok) break;
                     mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
-                    tma_load_2d_hint(smem_u32(st), &tmap_w, kb * SK_BKB, tile * SK_BM, full, pol_w);
+                    tma_load_2d_hint(smem_u32(st), &L.tmap_w, kb * SK_BKB, tile * SK_BM, full, pol_w);
                 }
-                tma_load_2d_hint(smem_u32(st + SK_W_BYTES), &tmap_x, kb * SK_BKB, 0, full, pol_x);
+                tma_load_2d_hint(smem_u32(st + SK_W_BYTES), &L.tmap_x, kb * SK_BKB, 0, full, pol_x);
                 if (++stage == SK_STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) {
@@ -209,9 +238,12 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
             int seg = 0;
             bool ok = true;
             long long u = u0;
+            int li = 0;
             while (u < u1 && ok) {
-                const int tile = (int)(u / num_kb);
-                long long seg_end = (long long)(tile + 1) * num_kb;
+                li = sk_seek(layers, count, u, li);
+                const long long lu = u - layers[li].unit0;
+                const int nkb = layers[li].num_kb;
+                long long seg_end = u + (nkb - lu % nkb);  // end of this (layer, tile)
                 if (seg_end > u1) seg_end = u1;
                 const int buf = seg & 1;
                 ok = mbar_wait(smem_u32(&bars->acc_empty[buf]), (uint32_t)(((seg >> 1) & 1) ^ 1),
@@ -249,9 +281,12 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
         int seg = 0;
         bool ok = true;
         long long u = u0;
+        int li = 0;
         while (u < u1 && ok) {
-            const int tile = (int)(u / num_kb);
-            const long long tile_u0 = (long long)tile * num_kb, tile_u1 = tile_u0 + num_kb;
+            li = sk_seek(layers, count, u, li);
+            const SkLayer &L = layers[li];
+            const int tile = (int)((u - L.unit0) / L.num_kb);
+            const long long tile_u0 = L.unit0 + (long long)tile * L.num_kb, tile_u1 = tile_u0 + L.num_kb;
             const long long seg_end = tile_u1 < u1 ? tile_u1 : u1;
             const bool whole = (u == tile_u0) && (seg_end == tile_u1);
             const int buf = seg & 1;
@@ -277,7 +312,7 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
 
             bool finish = whole;
             if (!whole) {
-                long long *dst = work.sums + ((size_t)tile * SK_ROWS) * SK_BM + ch_in_tile;
+                long long *dst = L.sums + ((size_t)tile * SK_ROWS) * SK_BM + ch_in_tile;
 #pragma unroll
                 for (int r = 0; r < 16; ++r)
                     if (r < m)
@@ -291,7 +326,7 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 if (lane == 0) {
                     const int parts = sk_cta_of(total, (int)gridDim.x, tile_u1 - 1) -
                                       sk_cta_of(total, (int)gridDim.x, tile_u0) + 1;
-                    const int ticket = atomicAdd(work.arrivals + tile * 4 + quarter, 1);
+                    const int ticket = atomicAdd(L.arrivals + tile * 4 + quarter, 1);
                     last = (ticket == parts - 1) ? 1 : 0;
                     __threadfence();
                 }
@@ -302,14 +337,17 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                         if (r < m) s[r] = __ldcg(dst + r * SK_BM);
                 }
             }
-            if (finish && ch < n) {
-                const float sc = __ldg(scales + ch);
+            if (finish && ch < L.n) {
+                const float sc = __ldg(L.scales + ch);
+                const float *bias = L.bias;
                 const float bv = bias ? __ldg(bias + ch) : 0.0f;
+                const float *unscale = L.unscale;
+                float *y = L.y;
+                const size_t ldy = L.ldy;
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
                     if (r < m) {
-                        float v = sk_finish(s[r], __ldg(work.unscale + 2 * r),
-                                            __ldg(work.unscale + 2 * r + 1), sc);
+                        float v = sk_finish(s[r], __ldg(unscale + 2 * r), __ldg(unscale + 2 * r + 1), sc);
                         if (bias) v = __fadd_rn(v, bv);
                         y[(size_t)r * ldy + ch] = v;
                     }
@@ -330,13 +368,13 @@ qlinear_skinny_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
     }
 }
 
-// Pre-pass.  Blocks 0..15: activation row r of x [m, k] (k % 16 == 0) -> three digit planes at
-// rows r, 16 + r, 32 + r of xd [48, k] and the row's 2^-e as two factors (rows >= m: zeros).
-// Same grid as the streaming GEMV: max|x| * 2^e in [2^19, 2^20).  Blocks >= 16 zero the partial-sum
-// workspace and the arrival counters.
+// Pre-pass.  Blocks 0 .. 16*count-1: activation row r = block % 16 of input block / 16, x [m, k]
+// (k % 16 == 0) -> three digit planes at rows r, 16 + r, 32 + r of xd [48, k] and the row's 2^-e as
+// two factors (rows >= m: zeros).  Same grid as the streaming GEMV: max|x| * 2^e in [2^19, 2^20).
+// The blocks after those zero the partial-sum workspace and the arrival counters.
 __global__ void __launch_bounds__(256)
-skinny_prepass_kernel(const float *__restrict__ x, int8_t *__restrict__ xd, float *__restrict__ unscale,
-                      int m, int k, uint4 *__restrict__ zero_base, size_t zero_count) {
+skinny_prepass_kernel(const __grid_constant__ SkInput one, const SkInput *__restrict__ many, int count,
+                      int m, uint4 *__restrict__ zero_base, size_t zero_count) {
     __shared__ float wmax[8];
     __shared__ int wbad[8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -344,13 +382,19 @@ skinny_prepass_kernel(const float *__restrict__ x, int8_t *__restrict__ xd, floa
     // in use by it: nothing is touched before that kernel has finished.
     grid_dependency_wait();
     grid_launch_dependents();
-    if (blockIdx.x >= SK_ROWS) {
-        const size_t nz = gridDim.x - SK_ROWS;
-        for (size_t i = (size_t)(blockIdx.x - SK_ROWS) * 256 + tid; i < zero_count; i += nz * 256)
+    const int row_blocks = SK_ROWS * count;
+    if ((int)blockIdx.x >= row_blocks) {
+        const size_t nz = gridDim.x - row_blocks;
+        for (size_t i = (size_t)(blockIdx.x - row_blocks) * 256 + tid; i < zero_count; i += nz * 256)
             zero_base[i] = make_uint4(0u, 0u, 0u, 0u);
         return;
     }
-    const int row = blockIdx.x;
+    const SkInput &in = many ? many[blockIdx.x / SK_ROWS] : one;
+    const int row = blockIdx.x % SK_ROWS;
+    const int k = in.k;
+    const float *x = in.x;
+    int8_t *xd = in.xd;
+    float *unscale = in.unscale;
     const int n4 = k >> 2;
     uint32_t *p0 = reinterpret_cast<uint32_t *>(xd + (size_t)row * k);
     uint32_t *p1 = reinterpret_cast<uint32_t *>(xd + (size_t)(SK_ROWS + row) * k);
@@ -457,61 +501,60 @@ void skinny_release_layer(nne_qlinear *ql) {
     ql->tmap_wsk = nullptr;
 }
 
-int launch_skinny(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy, cudaStream_t s) {
-    nne_ctx *ctx = ql->ctx;
+namespace {
+
+int set_smem_attr() {
     static bool attr_set = false;
     if (!attr_set) {
         NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_skinny_i8_kernel,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BYTES));
         attr_set = true;
     }
-    const size_t k = ql->k, n = ql->n;
-    const size_t tiles = (n + SK_BM - 1) / SK_BM;
-    const size_t num_kb = (k + SK_BKB - 1) / SK_BKB;
-    // stream-ordered workspace: [sums | arrivals] (zeroed by the pre-pass), unscale, digit planes
-    const size_t sums_bytes = tiles * SK_ROWS * SK_BM * sizeof(long long);
-    const size_t arr_bytes = (tiles * 4 * sizeof(int) + 255) & ~(size_t)255;
-    const size_t zero_bytes = sums_bytes + arr_bytes;  // a multiple of 16
-    const size_t uns_bytes = 256;
-    const size_t xd_bytes = (size_t)SK_N * k;
-    uint8_t *ws = nullptr;
-    NNE_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void **>(&ws), zero_bytes + uns_bytes + xd_bytes, s));
-    SkWork work;
-    work.sums = reinterpret_cast<long long *>(ws);
-    work.arrivals = reinterpret_cast<int *>(ws + sums_bytes);
-    float *unscale = reinterpret_cast<float *>(ws + zero_bytes);
-    work.unscale = unscale;
-    int8_t *xd = reinterpret_cast<int8_t *>(ws + zero_bytes + uns_bytes);
+    return NNE_OK;
+}
 
+size_t sk_tiles(size_t n) { return (n + SK_BM - 1) / SK_BM; }
+size_t sk_num_kb(size_t k) { return (k + SK_BKB - 1) / SK_BKB; }
+size_t sk_sums_bytes(size_t n) { return sk_tiles(n) * SK_ROWS * SK_BM * sizeof(long long); }
+size_t sk_arrivals_bytes(size_t n) { return (sk_tiles(n) * 4 * sizeof(int) + 255) & ~(size_t)255; }
+size_t sk_xd_bytes(size_t k) { return ((size_t)SK_N * k + 255) & ~(size_t)255; }
+
+// Fills everything of a layer's descriptor except the activation side and the work areas.
+void sk_fill_layer(SkLayer &L, const nne_qlinear *ql, float *y, size_t ldy) {
+    L.tmap_w = *static_cast<const CUtensorMap *>(ql->tmap_wsk);
+    L.scales = ql->scales;
+    L.bias = ql->bias;
+    L.y = y;
+    L.ldy = ldy;
+    L.n = (int)ql->n;
+    L.k = (int)ql->k;
+    L.num_kb = (int)sk_num_kb(ql->k);
+    L.tiles = (int)sk_tiles(ql->n);
+}
+
+int sk_launch(nne_ctx *ctx, const SkLayer *one, const SkLayer *many_dev, int count, const SkInput *in_one,
+              const SkInput *in_many_dev, int in_count, size_t m, long long total, uint4 *zero_base,
+              size_t zero_bytes, cudaStream_t s) {
+    NNE_TRY(set_smem_attr());
     cudaLaunchAttribute pdl[1];
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl[0].val.programmaticStreamSerializationAllowed = 1;
     {
         size_t zblocks = (zero_bytes / 16 + 2047) / 2048;  // 8 uint4 per thread
         if (zblocks < 1) zblocks = 1;
-        if (zblocks > 64) zblocks = 64;
+        if (zblocks > 128) zblocks = 128;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)(SK_ROWS + zblocks));
+        cfg.gridDim = dim3((unsigned)(SK_ROWS * in_count + zblocks));
         cfg.blockDim = dim3(256);
         cfg.stream = s;
         cfg.attrs = pdl;
         cfg.numAttrs = pdl_enabled() ? 1 : 0;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_prepass_kernel, x, xd, unscale, (int)m, (int)k,
-                                           reinterpret_cast<uint4 *>(ws), zero_bytes / 16);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, skinny_prepass_kernel, *in_one, in_many_dev, in_count,
+                                           (int)m, zero_base, zero_bytes / 16);
         count_launch();
-        if (e != cudaSuccess) {
-            cudaFreeAsync(ws, s);
+        if (e != cudaSuccess)
             return fail(NNE_ERR_CUDA, "skinny pre-pass launch failed: %s", cudaGetErrorString(e));
-        }
     }
-    CUtensorMap tmap_x;
-    int st = tma_make_map_2d(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xd, k, SK_N, SK_BKB, SK_N,
-                             CU_TENSOR_MAP_SWIZZLE_128B);
-    if (st != NNE_OK) {
-        cudaFreeAsync(ws, s);
-        return st;
-    }
-    const long long total = (long long)tiles * (long long)num_kb;
     int grid = ctx->sm_count;
     if (grid > total) grid = (int)total;
     cudaLaunchConfig_t cfg = {};
@@ -521,15 +564,165 @@ int launch_skinny(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ld
     cfg.stream = s;
     cfg.attrs = pdl;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, qlinear_skinny_i8_kernel,
-                                       *static_cast<const CUtensorMap *>(ql->tmap_wsk), tmap_x, work,
-                                       (const float *)ql->scales, (const float *)ql->bias, y, (int)m,
-                                       (int)n, (int)k, ldy, ctx->err_word);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, qlinear_skinny_i8_kernel, *one, many_dev, count, (int)m,
+                                       total, ctx->err_word);
     count_launch();
-    cudaFreeAsync(ws, s);
     if (e != cudaSuccess)
         return fail(NNE_ERR_CUDA, "skinny kernel launch failed: %s", cudaGetErrorString(e));
     return NNE_OK;
+}
+
+}  // namespace
+
+int launch_skinny(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy, cudaStream_t s) {
+    nne_ctx *ctx = ql->ctx;
+    const size_t k = ql->k, n = ql->n;
+    // stream-ordered workspace: [sums | arrivals] (zeroed by the pre-pass), unscale, digit planes
+    const size_t sums_bytes = sk_sums_bytes(n);
+    const size_t zero_bytes = sums_bytes + sk_arrivals_bytes(n);  // a multiple of 16
+    const size_t uns_bytes = 256;
+    uint8_t *ws = nullptr;
+    NNE_CUDA_TRY(cudaMallocAsync(reinterpret_cast<void **>(&ws), zero_bytes + uns_bytes + sk_xd_bytes(k), s));
+    SkInput in;
+    in.x = x;
+    in.unscale = reinterpret_cast<float *>(ws + zero_bytes);
+    in.xd = reinterpret_cast<int8_t *>(ws + zero_bytes + uns_bytes);
+    in.k = (int)k;
+    SkLayer L;
+    sk_fill_layer(L, ql, y, ldy);
+    L.sums = reinterpret_cast<long long *>(ws);
+    L.arrivals = reinterpret_cast<int *>(ws + sums_bytes);
+    L.unscale = in.unscale;
+    L.unit0 = 0;
+    int st = tma_make_map_2d(&L.tmap_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, in.xd, k, SK_N, SK_BKB, SK_N,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (st == NNE_OK)
+        st = sk_launch(ctx, &L, nullptr, 1, &in, nullptr, 1, m, (long long)L.tiles * L.num_kb,
+                       reinterpret_cast<uint4 *>(ws), zero_bytes, s);
+    cudaFreeAsync(ws, s);
+    return st;
+}
+
+// ---- plan: several layers in one launch ------------------------------------------------------------
+// The plan owns its work areas (partial sums, counters, digit planes) and the device copies of
+// the descriptors, all allocated once at creation: a run allocates nothing.  Layers that read
+// the same x (q/k/v, gate/up) share one set of digit planes.
+struct SkPlan {
+    nne_ctx *ctx = nullptr;
+    uint8_t *ws = nullptr;
+    SkLayer *layers_dev = nullptr;
+    SkInput *inputs_dev = nullptr;
+    SkLayer first_layer;   // passed by value too (the kernel's parameter block wants one)
+    SkInput first_input;
+    int count = 0, in_count = 0;
+    size_t m = 0, zero_bytes = 0;
+    long long total = 0;
+};
+
+bool skinny_plan_supports(nne_qlinear *const *layers, const float *const *x, float *const *y,
+                          size_t count, size_t m) {
+    if (count == 0 || count > 4096) return false;
+    for (size_t i = 0; i < count; ++i) {
+        if (!skinny_supports(layers[i], m)) return false;
+        if ((reinterpret_cast<uintptr_t>(x[i]) & 15u) || (reinterpret_cast<uintptr_t>(y[i]) & 3u)) return false;
+    }
+    return true;
+}
+
+int skinny_plan_create(nne_ctx *ctx, nne_qlinear *const *layers, const float *const *x, float *const *y,
+                       size_t count, size_t m, SkPlan **out) {
+    *out = nullptr;
+    std::unique_ptr<SkPlan> plan(new SkPlan());
+    plan->ctx = ctx;
+    plan->count = (int)count;
+    plan->m = m;
+    // distinct inputs
+    std::vector<int> input_of(count);
+    std::vector<SkInput> inputs;
+    for (size_t i = 0; i < count; ++i) {
+        int found = -1;
+        for (size_t j = 0; j < inputs.size(); ++j)
+            if (inputs[j].x == x[i] && (size_t)inputs[j].k == layers[i]->k) found = (int)j;
+        if (found < 0) {
+            SkInput in;
+            in.x = x[i];
+            in.xd = nullptr;
+            in.unscale = nullptr;
+            in.k = (int)layers[i]->k;
+            inputs.push_back(in);
+            found = (int)inputs.size() - 1;
+        }
+        input_of[i] = found;
+    }
+    plan->in_count = (int)inputs.size();
+    // one allocation: [sums and arrivals of every layer | unscale per input | digit planes per input]
+    size_t zero_bytes = 0;
+    for (size_t i = 0; i < count; ++i) zero_bytes += sk_sums_bytes(layers[i]->n) + sk_arrivals_bytes(layers[i]->n);
+    size_t bytes = zero_bytes + 256 * inputs.size();
+    for (const SkInput &in : inputs) bytes += sk_xd_bytes((size_t)in.k);
+    NNE_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&plan->ws), bytes));
+    struct Guard {
+        SkPlan *p;
+        ~Guard() {
+            if (!p) return;
+            cudaFree(p->ws);
+            cudaFree(p->layers_dev);
+            cudaFree(p->inputs_dev);
+        }
+    } guard{plan.get()};
+    plan->zero_bytes = zero_bytes;
+    uint8_t *cur = plan->ws + zero_bytes;
+    for (SkInput &in : inputs) {
+        in.unscale = reinterpret_cast<float *>(cur);
+        cur += 256;
+    }
+    std::vector<CUtensorMap> xmaps(inputs.size());
+    for (size_t j = 0; j < inputs.size(); ++j) {
+        inputs[j].xd = reinterpret_cast<int8_t *>(cur);
+        cur += sk_xd_bytes((size_t)inputs[j].k);
+        NNE_TRY(tma_make_map_2d(&xmaps[j], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, inputs[j].xd, (size_t)inputs[j].k,
+                                SK_N, SK_BKB, SK_N, CU_TENSOR_MAP_SWIZZLE_128B));
+    }
+    std::vector<SkLayer> descs(count);
+    uint8_t *z = plan->ws;
+    long long unit = 0;
+    for (size_t i = 0; i < count; ++i) {
+        SkLayer &L = descs[i];
+        sk_fill_layer(L, layers[i], y[i], layers[i]->n);
+        L.tmap_x = xmaps[input_of[i]];
+        L.unscale = inputs[input_of[i]].unscale;
+        L.sums = reinterpret_cast<long long *>(z);
+        z += sk_sums_bytes(layers[i]->n);
+        L.arrivals = reinterpret_cast<int *>(z);
+        z += sk_arrivals_bytes(layers[i]->n);
+        L.unit0 = unit;
+        unit += (long long)L.tiles * L.num_kb;
+    }
+    plan->total = unit;
+    NNE_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&plan->layers_dev), count * sizeof(SkLayer)));
+    NNE_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&plan->inputs_dev), inputs.size() * sizeof(SkInput)));
+    NNE_CUDA_TRY(cudaMemcpy(plan->layers_dev, descs.data(), count * sizeof(SkLayer), cudaMemcpyHostToDevice));
+    NNE_CUDA_TRY(cudaMemcpy(plan->inputs_dev, inputs.data(), inputs.size() * sizeof(SkInput),
+                            cudaMemcpyHostToDevice));
+    plan->first_layer = descs[0];
+    plan->first_input = inputs[0];
+    guard.p = nullptr;
+    *out = plan.release();
+    return NNE_OK;
+}
+
+int skinny_plan_run(SkPlan *plan, cudaStream_t s) {
+    return sk_launch(plan->ctx, &plan->first_layer, plan->layers_dev, plan->count, &plan->first_input,
+                     plan->inputs_dev, plan->in_count, plan->m, plan->total,
+                     reinterpret_cast<uint4 *>(plan->ws), plan->zero_bytes, s);
+}
+
+void skinny_plan_destroy(SkPlan *plan) {
+    if (!plan) return;
+    cudaFree(plan->ws);
+    cudaFree(plan->layers_dev);
+    cudaFree(plan->inputs_dev);
+    delete plan;
 }
 
 }  // namespace nne

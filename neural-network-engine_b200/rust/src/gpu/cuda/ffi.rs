@@ -7,6 +7,10 @@ pub struct nne_ctx {
     _private: [u8; 0],
 }
 #[repr(C)]
+pub struct nne_plan {
+    _private: [u8; 0],
+}
+#[repr(C)]
 pub struct nne_qlinear {
     _private: [u8; 0],
 }
@@ -90,4 +94,30 @@ extern "C" {
         y_dev: *mut f32,
         stream: *mut c_void,
     ) -> c_int;
+    pub fn nne_qlinear_forward_dev_strided(
+        ql: *mut nne_qlinear,
+        x_dev: *const f32,
+        m: usize,
+        k: usize,
+        y_dev: *mut f32,
+        ldy: usize,
+        stream: *mut c_void,
+    ) -> c_int;
+    pub fn nne_qlinear_kernel_for(ql: *const nne_qlinear, m: usize) -> c_int;
+    pub fn nne_cuda_ctx_reserve_sms(ctx: *mut nne_ctx, count: c_int) -> c_int;
+
+    // Several independent projections (q/k/v at src/models/llama.rs:226-228) as one launch.
+    pub fn nne_qlinear_plan_create(
+        ctx: *mut nne_ctx,
+        count: usize,
+        layers: *const *mut nne_qlinear,
+        x_dev: *const *const f32,
+        y_dev: *const *mut f32,
+        m: usize,
+        out: *mut *mut nne_plan,
+    ) -> c_int;
+    pub fn nne_qlinear_plan_run(plan: *mut nne_plan, stream: *mut c_void) -> c_int;
+    pub fn nne_qlinear_plan_run_host(plan: *mut nne_plan, x_all_host: *const f32, y_all_host: *mut f32) -> c_int;
+    pub fn nne_qlinear_plan_launches(plan: *const nne_plan) -> c_int;
+    pub fn nne_qlinear_plan_destroy(plan: *mut nne_plan) -> c_int;
 }

@@ -102,3 +102,47 @@ def test_plan_run_host_equals_single_forwards(nne, ctx, m, slabs):
         off += single.size
     with pytest.raises(nne.ShapeMismatch):
         plan.run_host(x_all[:-1])
+
+
+@pytest.mark.parametrize("m", [3, 8, 16])
+@pytest.mark.parametrize("shared", [False, True])
+def test_small_batch_plan_equals_single_forwards(nne, ctx, m, shared):
+    """3 <= m <= 16: the list runs as one pre-pass + one small-batch tensor-core launch.  With
+    `shared`, the first three layers read the same x (q/k/v) and the last two another (gate/up)."""
+    import torch
+    shapes = [(512, 1024, True), (300, 1024, False), (1024, 1024, True), (2048, 512, False),
+              (130, 512, True)]
+    layers, xs, ys, refs = build(nne, ctx, shapes, m, 120 + m)
+    if shared:
+        xs = [xs[0], xs[0], xs[0], xs[3], xs[3]]
+        refs = [(refs[i][0], refs[0][1] if i < 3 else refs[3][1], refs[i][2]) for i in range(5)]
+    plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], m, ctx)
+    assert plan.launches == 2
+    s = torch.cuda.current_stream().cuda_stream
+    plan.run(s)
+    plan.run(s)
+    torch.cuda.synchronize()
+    ctx.check()
+    for (ql, x, b), y in zip(refs, ys):
+        single = ql.forward(x)
+        got = y.cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), single.view(np.uint32))
+        qw = ql.qweight.reshape(ql.out_features, ql.in_features)
+        tol, _ = oracle.tolerance(qw, ql.scales, x)
+        y_ref = oracle.forward(qw, ql.scales, b, x)
+        assert float((np.abs(got - y_ref) / tol).max()) <= 1e-2
+
+
+def test_small_batch_plan_many_layers_big_shapes(nne, ctx):
+    """More units than one CTA range per layer and more layers than SMs' worth of tiles: 7B-shaped
+    q/k/v/o + gate/up + down as one list at m = 8."""
+    import torch
+    shapes = [(4096, 4096, False)] * 4 + [(11008, 4096, False)] * 2 + [(4096, 11008, True)]
+    layers, xs, ys, refs = build(nne, ctx, shapes, 8, 131)
+    plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], 8, ctx)
+    assert plan.launches == 2
+    plan.run(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    ctx.check()
+    for (ql, x, b), y in zip(refs, ys):
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), ql.forward(x).view(np.uint32))
