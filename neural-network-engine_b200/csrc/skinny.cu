@@ -134,11 +134,32 @@ __device__ __forceinline__ float sk_finish(long long s, float u0, float u1, floa
     return __fmul_rn(dot, scale);
 }
 
-// Layer that holds unit u, searching forward from li (units are visited in increasing order).
-__device__ __forceinline__ int sk_seek(const SkLayer *layers, int count, long long u, int li) {
-    while (li + 1 < count && u >= layers[li + 1].unit0) ++li;
-    return li;
+// The layer a role is working in, with the scalars it needs per unit held in registers: the
+// descriptor itself sits in the parameter block or in global memory and is read only when the
+// unit index crosses into another layer (units are visited in increasing order).
+struct SkCur {
+    long long unit0 = 0, end = 0;  // units [unit0, end) belong to layer li
+    int num_kb = 1, li = -1;
+};
+__device__ __forceinline__ void sk_seek(const SkLayer &one, const SkLayer *many, int count,
+                                        long long u, SkCur &c) {
+    if (u < c.end) return;
+    if (!many) {  // a single forward: the parameter block is read directly, not through a pointer
+        c.li = 0;
+        c.unit0 = 0;
+        c.num_kb = one.num_kb;
+        c.end = (long long)one.tiles * one.num_kb;
+        return;
+    }
+    int li = c.li < 0 ? 0 : c.li;
+    while (li + 1 < count && u >= many[li + 1].unit0) ++li;
+    c.li = li;
+    c.unit0 = many[li].unit0;
+    c.num_kb = many[li].num_kb;
+    c.end = c.unit0 + (long long)many[li].tiles * c.num_kb;
 }
+// Field f of the current layer.
+#define SK_FIELD(f) (many ? many[c.li].f : one.f)
 
 __global__ void __launch_bounds__(SK_THREADS, 1)
 qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__restrict__ many,
@@ -148,7 +169,6 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     SkBars *bars = reinterpret_cast<SkBars *>(smem + SK_STAGES * SK_STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const SkLayer *layers = many ? many : &one;
     long long u0, u1;
     sk_range(total, (int)blockIdx.x, (int)gridDim.x, u0, u1);
     volatile int *abort_flag = &bars->abort_flag;
@@ -184,28 +204,29 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
             const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
             // Weights never change after the layer is created: the ring's first round of weight
             // tiles is requested before waiting for the pre-pass that writes the digit planes.
-            int pre = 0, li = sk_seek(layers, count, u0, 0);
+            int pre = 0;
+            SkCur c;
             for (; pre < SK_STAGES && u0 + pre < u1; ++pre) {
                 const long long u = u0 + pre;
-                li = sk_seek(layers, count, u, li);
-                const SkLayer &L = layers[li];
-                const long long lu = u - L.unit0;
-                const int tile = (int)(lu / L.num_kb), kb = (int)(lu % L.num_kb);
+                sk_seek(one, many, count, u, c);
+                const int lu = (int)(u - c.unit0);
+                const int tile = lu / c.num_kb, kb = lu % c.num_kb;
                 const uint32_t full = smem_u32(&bars->full[pre]);
                 mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
-                tma_load_2d_hint(smem_u32(smem + pre * SK_STAGE_BYTES), &L.tmap_w, kb * SK_BKB,
+                tma_load_2d_hint(smem_u32(smem + pre * SK_STAGE_BYTES), (many ? &many[c.li].tmap_w : &one.tmap_w), kb * SK_BKB,
                                  tile * SK_BM, full, pol_w);
             }
             grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            li = sk_seek(layers, count, u0, 0);
+            c = SkCur();
             for (long long u = u0; u < u1; ++u) {
-                li = sk_seek(layers, count, u, li);
-                const SkLayer &L = layers[li];
-                const long long lu = u - L.unit0;
-                const int tile = (int)(lu / L.num_kb), kb = (int)(lu % L.num_kb);
+                sk_seek(one, many, count, u, c);
+                const CUtensorMap *map_w = many ? &many[c.li].tmap_w : &one.tmap_w;
+                const CUtensorMap *map_x = many ? &many[c.li].tmap_x : &one.tmap_x;
+                const int lu = (int)(u - c.unit0);
+                const int tile = lu / c.num_kb, kb = lu % c.num_kb;
                 uint8_t *st = smem + stage * SK_STAGE_BYTES;
                 const uint32_t full = smem_u32(&bars->full[stage]);
                 if (pre > 0) {
@@ -214,9 +235,9 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
                     ok = mbar_wait(smem_u32(&bars->empty[stage]), phase ^ 1, abort_flag, err, 0x31);
                     if (!ok) break;
                     mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
-                    tma_load_2d_hint(smem_u32(st), &L.tmap_w, kb * SK_BKB, tile * SK_BM, full, pol_w);
+                    tma_load_2d_hint(smem_u32(st), map_w, kb * SK_BKB, tile * SK_BM, full, pol_w);
                 }
-                tma_load_2d_hint(smem_u32(st + SK_W_BYTES), &L.tmap_x, kb * SK_BKB, 0, full, pol_x);
+                tma_load_2d_hint(smem_u32(st + SK_W_BYTES), map_x, kb * SK_BKB, 0, full, pol_x);
                 if (++stage == SK_STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) {
@@ -238,12 +259,11 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
             int seg = 0;
             bool ok = true;
             long long u = u0;
-            int li = 0;
+            SkCur c;
             while (u < u1 && ok) {
-                li = sk_seek(layers, count, u, li);
-                const long long lu = u - layers[li].unit0;
-                const int nkb = layers[li].num_kb;
-                long long seg_end = u + (nkb - lu % nkb);  // end of this (layer, tile)
+                sk_seek(one, many, count, u, c);
+                const int lu = (int)(u - c.unit0);
+                long long seg_end = u + (c.num_kb - lu % c.num_kb);  // end of this (layer, tile)
                 if (seg_end > u1) seg_end = u1;
                 const int buf = seg & 1;
                 ok = mbar_wait(smem_u32(&bars->acc_empty[buf]), (uint32_t)(((seg >> 1) & 1) ^ 1),
@@ -281,15 +301,29 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
         int seg = 0;
         bool ok = true;
         long long u = u0;
-        int li = 0;
+        SkCur c;
         while (u < u1 && ok) {
-            li = sk_seek(layers, count, u, li);
-            const SkLayer &L = layers[li];
-            const int tile = (int)((u - L.unit0) / L.num_kb);
-            const long long tile_u0 = L.unit0 + (long long)tile * L.num_kb, tile_u1 = tile_u0 + L.num_kb;
+            sk_seek(one, many, count, u, c);
+            const int tile = (int)(u - c.unit0) / c.num_kb;
+            const long long tile_u0 = c.unit0 + (long long)tile * c.num_kb, tile_u1 = tile_u0 + c.num_kb;
             const long long seg_end = tile_u1 < u1 ? tile_u1 : u1;
             const bool whole = (u == tile_u0) && (seg_end == tile_u1);
             const int buf = seg & 1;
+            // Everything the segment needs from the descriptor and from global memory is fetched
+            // before the wait, so that only the TMEM read and the reduction follow the MMAs.
+            const int ch = tile * SK_BM + ch_in_tile;
+            const int n = SK_FIELD(n);
+            long long *dst = SK_FIELD(sums) + ((size_t)tile * SK_ROWS) * SK_BM + ch_in_tile;
+            int *ticket_word = SK_FIELD(arrivals) + tile * 4 + quarter;
+            const float *bias = SK_FIELD(bias);
+            const float *unscale = SK_FIELD(unscale);
+            float *y = SK_FIELD(y);
+            const size_t ldy = SK_FIELD(ldy);
+            const float sc = (ch < n) ? __ldg(SK_FIELD(scales) + ch) : 0.0f;
+            const float bv = (bias && ch < n) ? __ldg(bias + ch) : 0.0f;
+            const int parts = whole ? 1
+                                    : sk_cta_of(total, (int)gridDim.x, tile_u1 - 1) -
+                                          sk_cta_of(total, (int)gridDim.x, tile_u0) + 1;
             ok = mbar_wait(smem_u32(&bars->acc_full[buf]), (uint32_t)((seg >> 1) & 1), abort_flag, err,
                            0x34);
             if (!ok) break;
@@ -304,7 +338,6 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->acc_empty[buf]));
 
-            const int ch = tile * SK_BM + ch_in_tile;
             long long s[16];
 #pragma unroll
             for (int r = 0; r < 16; ++r)
@@ -312,7 +345,6 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
 
             bool finish = whole;
             if (!whole) {
-                long long *dst = L.sums + ((size_t)tile * SK_ROWS) * SK_BM + ch_in_tile;
 #pragma unroll
                 for (int r = 0; r < 16; ++r)
                     if (r < m)
@@ -324,9 +356,7 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
                 __syncwarp();
                 int last = 0;
                 if (lane == 0) {
-                    const int parts = sk_cta_of(total, (int)gridDim.x, tile_u1 - 1) -
-                                      sk_cta_of(total, (int)gridDim.x, tile_u0) + 1;
-                    const int ticket = atomicAdd(L.arrivals + tile * 4 + quarter, 1);
+                    const int ticket = atomicAdd(ticket_word, 1);
                     last = (ticket == parts - 1) ? 1 : 0;
                     __threadfence();
                 }
@@ -337,13 +367,7 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
                         if (r < m) s[r] = __ldcg(dst + r * SK_BM);
                 }
             }
-            if (finish && ch < L.n) {
-                const float sc = __ldg(L.scales + ch);
-                const float *bias = L.bias;
-                const float bv = bias ? __ldg(bias + ch) : 0.0f;
-                const float *unscale = L.unscale;
-                float *y = L.y;
-                const size_t ldy = L.ldy;
+            if (finish && ch < n) {
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
                     if (r < m) {

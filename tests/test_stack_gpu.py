@@ -104,6 +104,45 @@ def test_config4_decoder_stack(nne, ctx):
         dt = time.perf_counter() - t0
         print(f"config4 batch {b}: {dt * 1e3:.2f} ms per decode step of the linear layers, "
               f"{b / dt:.0f} tokens/s, {total_bytes / dt / 1e9:.0f} GB/s of weights")
+    # The same step with the independent projections of a layer grouped into plans
+    # ([q, k, v], [o], [gate, up], [down]: 4 launches or launch pairs per layer instead of 7);
+    # the result must not change by a bit.
+    for b in (1, 8):
+        xb = x8[:b].contiguous()
+        want = decode_step(xb)
+        bufs = {name: torch.empty(b, n, device=dev) for name, n, _ in NAMES}
+        hid = [torch.empty(b, H, device=dev), torch.empty(b, H, device=dev)]
+        plans = []
+        for li, layer in enumerate(stack):
+            src, dst = hid[li % 2], hid[(li + 1) % 2]
+            groups = [(("q", "k", "v"), src, None), (("o",), bufs["q"], None),
+                      (("gate", "up"), bufs["o"], None), (("down",), bufs["gate"], dst)]
+            for names, xin, out in groups:
+                cnt = len(names)
+                hs = (C.c_void_p * cnt)(*[layer[nm] for nm in names])
+                xs = (C.c_void_p * cnt)(*[xin.data_ptr()] * cnt)
+                ys = (C.c_void_p * cnt)(*[(out if out is not None else bufs[nm]).data_ptr() for nm in names])
+                p = C.c_void_p()
+                assert lib.nne_qlinear_plan_create(ctx.handle, cnt, hs, xs, ys, b, C.byref(p)) == 0
+                plans.append(p)
+
+        def plan_step():
+            hid[0].copy_(xb)
+            for p in plans:
+                assert lib.nne_qlinear_plan_run(p, stream) == 0
+            torch.cuda.synchronize()
+            return hid[LAYERS % 2]
+
+        got = plan_step()
+        ctx.check()
+        assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+        t0 = time.perf_counter()
+        plan_step()
+        dt = time.perf_counter() - t0
+        print(f"config4 batch {b}, grouped into plans: {dt * 1e3:.2f} ms per decode step, "
+              f"{b / dt:.0f} tokens/s, {total_bytes / dt / 1e9:.0f} GB/s of weights")
+        for p in plans:
+            lib.nne_qlinear_plan_destroy(p)
     for layer in stack:
         for h in layer.values():
             lib.nne_qlinear_destroy(h)
