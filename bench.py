@@ -436,7 +436,7 @@ def run_native(args):
     # decode batch sweep (config 2): one forward per layer over the rotation set, M rows each
     sweep = None
     if world == 1:
-        sweep = run_decode_sweep(nne, lib, dev, layers, args)
+        sweep = run_decode_sweep(nne, lib, ctx, dev, layers, args)
 
     # prefill (M = 2048) on the tensor-core kernel, when it is built in
     prefill = None
@@ -494,9 +494,10 @@ def run_native(args):
         dist.destroy_process_group()
 
 
-def run_decode_sweep(nne, lib, dev, layers, args):
-    """M in {1, 2, 4, 8, 16}: forwards of the 12-layer rotation set issued one layer at a time,
-    back to back on one stream; GB/s = algorithmic bytes / device time."""
+def run_decode_sweep(nne, lib, ctx, dev, layers, args):
+    """M in {1, 2, 4, 8, 16}: forwards of the 12-layer rotation set, (a) issued one layer at a time
+    back to back on one stream, (b) as one plan over the 12 layers; GB/s = algorithmic bytes /
+    device time."""
     import torch
     stream = torch.cuda.current_stream()
     cases = []
@@ -523,10 +524,34 @@ def run_decode_sweep(nne, lib, dev, layers, args):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / iters
         nbytes = sum(algorithmic_bytes(L["n"], L["k"], m) for L in layers)
+        launches = (lib.nne_launch_count() - l0) / (iters * len(layers))
+        # (b) the same 12 forwards as one plan
+        nl = len(layers)
+        plan = C.c_void_p()
+        if lib.nne_qlinear_plan_create(ctx.handle, nl, (C.c_void_p * nl)(*[L["h"] for L in layers]),
+                                       (C.c_void_p * nl)(*[x.data_ptr() for x in xs]),
+                                       (C.c_void_p * nl)(*[y.data_ptr() for y in ys]), m, C.byref(plan)) != 0:
+            raise RuntimeError(nne._lib.last_error())
+        for _ in range(3):
+            lib.nne_qlinear_plan_run(plan, stream.cuda_stream)
+        torch.cuda.synchronize()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record(stream)
+        for _ in range(iters):
+            if lib.nne_qlinear_plan_run(plan, stream.cuda_stream) != 0:
+                raise RuntimeError(nne._lib.last_error())
+        p1.record(stream)
+        torch.cuda.synchronize()
+        pms = p0.elapsed_time(p1) / iters
+        plan_launches = lib.nne_qlinear_plan_launches(plan)
+        lib.nne_qlinear_plan_destroy(plan)
         cases.append({"m": m, "GB/s": nbytes / (ms * 1e-3) / 1e9, "us_per_layer": ms * 1e3 / len(layers),
                       "kernel": int(lib.nne_qlinear_kernel_for(layers[0]["h"], m)),
-                      "launches_per_layer": (lib.nne_launch_count() - l0) / (iters * len(layers))})
-    return {"cases": cases, "launch": "one forward per layer, back to back (no plan, no graph)",
+                      "launches_per_layer": launches,
+                      "plan_GB/s": nbytes / (pms * 1e-3) / 1e9, "plan_us_per_step": pms * 1e3,
+                      "plan_launches_per_step": int(plan_launches)})
+    return {"cases": cases, "launch": "GB/s: one forward per layer, back to back (no plan, no graph); "
+                                      "plan_GB/s: the 12 forwards as one plan",
             "kernels": {"1": "qgemv_stream_kernel", "4": "qlinear_skinny_i8_kernel"}}
 
 

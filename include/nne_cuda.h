@@ -174,9 +174,9 @@ NNE_API int nne_qlinear_forward_dev_static(nne_qlinear *ql, const float *x_dev, 
  * the place of the back-to-back QLinear::forward calls a caller makes on projections that do
  * not depend on each other - q/k/v (src/models/llama.rs:226-228), gate/up
  * (src/models/llama.rs:344-346), or the per-layer timing loop of the decode benchmark - each
- * of which is the contraction of src/nn/quantized.rs:164-193.  For m <= 2 and streaming-capable
+ * of which is the contraction of src/nn/quantized.rs:164-193.  For m = 1 and streaming-capable
  * shapes the whole list is ONE kernel launch whose weight stream never drains between layers;
- * for 3 <= m <= 16 it is one pre-pass and one launch of the small-batch tensor-core kernel over
+ * for 2 <= m <= 16 it is one pre-pass and one launch of the small-batch tensor-core kernel over
  * all layers (layers given the same x pointer share one set of digit planes; the work areas are
  * allocated at creation, so a run allocates nothing; a plan must not run concurrently with
  * itself); otherwise the plan runs its layers one after the other.  Results are identical to

@@ -657,9 +657,9 @@ int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *laye
                 gemv_tma_supports(ql->n, ql->k, m);
     }
     plan->fused = fused && count > 0;
-    if (!plan->fused && m >= 3 && !skinny_disabled() &&
-        skinny_plan_supports(layers, x_dev, y_dev, count, m)) {
+    if (m >= 2 && !skinny_disabled() && skinny_plan_supports(layers, x_dev, y_dev, count, m)) {
         NNE_TRY(skinny_plan_create(ctx, layers, x_dev, y_dev, count, m, &plan->skinny));
+        plan->fused = false;
     }
     if (plan->fused && count > (size_t)STREAM_INLINE_LAYERS) {
         NNE_CUDA_TRY(cudaMalloc(&plan->descs_dev, count * sizeof(StreamLayer)));

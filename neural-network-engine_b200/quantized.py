@@ -321,7 +321,8 @@ class QLinearPlan:
     Stands for the back-to-back ``forward`` calls a caller makes on projections that do not depend
     on each other (q/k/v at src/models/llama.rs:226-228, gate/up at :344-346).  ``x_ptrs[i]`` is a
     device pointer to ``[m, layers[i].in_features]`` f32, ``y_ptrs[i]`` to ``[m, out_features]``.
-    For m <= 2 the whole list is one kernel launch; results equal per-layer ``forward_device``."""
+    For m = 1 the whole list is one kernel launch, for 2 <= m <= 16 one pre-pass and one launch;
+    results equal per-layer ``forward_device`` bit for bit."""
 
     def __init__(self, layers, x_ptrs, y_ptrs, m: int, ctx: Optional[CudaContext] = None):
         ctx = ctx or layers[0]._ctx or default_context()
