@@ -1,11 +1,14 @@
 """A plan runs several independent forwards as one launch; its results must be bit-identical to
 the same forwards issued one by one (and therefore inherit their parity with the oracle)."""
+import os
+
 import numpy as np
 import pytest
 
 import oracle
 
 pytestmark = pytest.mark.gpu
+SKINNY_OFF = os.environ.get("NNE_SKINNY", "").startswith("0")  # small-batch kernel switched off
 
 
 def build(nne, ctx, shapes, m, seed):
@@ -33,7 +36,7 @@ def test_plan_equals_single_forwards(nne, ctx, shapes, m):
     layers, xs, ys, refs = build(nne, ctx, shapes, m, 90 + m)
     plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], m, ctx)
     # m = 1: one streaming-GEMV launch; m = 2: pre-pass + one small-batch tensor-core launch
-    assert plan.launches == m
+    assert plan.launches == (1 if SKINNY_OFF else m)
     s = torch.cuda.current_stream().cuda_stream
     plan.run(s)
     plan.run(s)  # twice: the second run must not depend on state left by the first
@@ -118,7 +121,7 @@ def test_small_batch_plan_equals_single_forwards(nne, ctx, m, shared):
         xs = [xs[0], xs[0], xs[0], xs[3], xs[3]]
         refs = [(refs[i][0], refs[0][1] if i < 3 else refs[3][1], refs[i][2]) for i in range(5)]
     plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], m, ctx)
-    assert plan.launches == 2
+    assert plan.launches == (len(layers) if SKINNY_OFF else 2)
     s = torch.cuda.current_stream().cuda_stream
     plan.run(s)
     plan.run(s)
@@ -141,7 +144,7 @@ def test_small_batch_plan_many_layers_big_shapes(nne, ctx):
     shapes = [(4096, 4096, False)] * 4 + [(11008, 4096, False)] * 2 + [(4096, 11008, True)]
     layers, xs, ys, refs = build(nne, ctx, shapes, 8, 131)
     plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], 8, ctx)
-    assert plan.launches == 2
+    assert plan.launches == (len(layers) if SKINNY_OFF else 2)
     plan.run(torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     ctx.check()

@@ -5,12 +5,16 @@ The kernel puts each activation row on the same fixed-point grid as the streamin
 tolerance check against the oracle there are two bit-for-bit checks: integer-valued activations
 against the oracle, and every row of a batch against the single-row forward of that row (which
 runs the streaming GEMV, a different kernel)."""
+import os
+
 import numpy as np
 import pytest
 
 import oracle
 
-pytestmark = pytest.mark.gpu
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(os.environ.get("NNE_SKINNY", "").startswith("0"),
+                                 reason="the small-batch kernel is switched off (NNE_SKINNY=0)")]
 
 
 def layer(nne, ctx, seed, n, k, bias):
