@@ -31,17 +31,27 @@
 namespace nne {
 namespace {
 
-constexpr int BM = 128, BN = 256, BKB = 128;  // BKB: bytes (= int8 elements) of K per k-block
-constexpr int STAGES = 3;
-constexpr int W_BYTES = BN * BKB;   // 32 KB
+constexpr int BM = 128, BKB = 128;  // BKB: bytes (= int8 elements) of K per k-block
+constexpr int MAX_STAGES = 4;
 constexpr int X_BYTES = BM * BKB;   // 16 KB per digit
-constexpr int STAGE_BYTES = W_BYTES + 2 * X_BYTES;  // 64 KB
 constexpr int BAR_BYTES = 256;
 constexpr int NUM_EPI_WARPS = 8;  // two per TMEM lane quarter, each takes half of the columns
 constexpr int EPI_STAGE_BYTES = 32 * 32 * 4;  // one 32x32 f32 block per epilogue warp
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + NUM_EPI_WARPS * EPI_STAGE_BYTES + BAR_BYTES + 1024;
+// Output tiles are 128 x BN with BN = 256 (3 stages of 64 KB) or, when that would leave SMs idle
+// or the last round of tiles mostly empty, BN = 128 (4 stages of 48 KB).
+template <int BN>
+struct Cfg {
+    static constexpr int STAGES = BN == 256 ? 3 : 4;
+    static constexpr int W_BYTES = BN * BKB;
+    static constexpr int STAGE_BYTES = W_BYTES + 2 * (BM * BKB);
+    static constexpr int SMEM_BYTES =
+        STAGES * STAGE_BYTES + NUM_EPI_WARPS * (32 * 32 * 4) + BAR_BYTES + 1024;
+    static constexpr uint32_t TMEM_COLS = 2 * BN;  // two int32 accumulators of BN columns
+    // Instruction descriptor: D = s32, A = B = signed int8, both K-major, M = 128, N = BN.
+    static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                      ((uint32_t)(BM >> 4) << 24);
+};
 constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
-constexpr uint32_t TMEM_COLS = 512;  // two int32 accumulators of 256 columns
 
 __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -52,19 +62,15 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: D = s32, A = B = signed int8, both K-major, M = 128, N = 256.
-constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                              ((uint32_t)(BM >> 4) << 24);
-
 __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                        uint32_t accumulate) {
+                                        uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n"
         ".reg .pred p;\n"
         "setp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
         "}\n" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(IDESC_I8), "r"(accumulate)
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -82,8 +88,8 @@ __device__ __forceinline__ float combine(uint32_t d0, uint32_t d1) {
 }
 
 struct Bars {
-    uint64_t full[STAGES];
-    uint64_t empty[STAGES];
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
     uint64_t acc_full;
     uint64_t acc_empty;
     uint32_t tmem_base;
@@ -91,6 +97,7 @@ struct Bars {
 };
 static_assert(sizeof(Bars) <= BAR_BYTES, "barrier block too large");
 
+template <int BN>
 __global__ void __launch_bounds__(THREADS, 1)
 qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_x0,
@@ -98,6 +105,9 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                           const float *__restrict__ unscale, const float *__restrict__ scales,
                           const float *__restrict__ bias, float *__restrict__ y, int m, int n, int k,
                           size_t ldy, int tiles_m, int num_tiles, int *err) {
+    constexpr int STAGES = Cfg<BN>::STAGES, W_BYTES = Cfg<BN>::W_BYTES,
+                  STAGE_BYTES = Cfg<BN>::STAGE_BYTES;
+    constexpr uint32_t TMEM_COLS = Cfg<BN>::TMEM_COLS, IDESC = Cfg<BN>::IDESC;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -201,8 +211,8 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     for (int kk = 0; kk < BKB / 32; ++kk) {
                         // +32 bytes per 32-element k step inside the 128-byte swizzle span
                         const uint32_t accum = (kb | kk) != 0 ? 1u : 0u;
-                        umma_i8(tmem_base, x0_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), accum);
-                        umma_i8(tmem_base + BN, x1_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), accum);
+                        umma_i8(tmem_base, x0_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), IDESC, accum);
+                        umma_i8(tmem_base + BN, x1_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), IDESC, accum);
                     }
                     umma_commit(smem_u32(&bars->empty[stage]));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -407,6 +417,15 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
 
 }  // namespace
 
+// NNE_PREFILL_TILE=256 keeps the wide tile for every shape.
+static bool prefill_wide_forced() {
+    static const bool v = []() {
+        const char *e = getenv("NNE_PREFILL_TILE");
+        return e && e[0] == '2';
+    }();
+    return v;
+}
+
 bool prefill_i8_supports(const nne_qlinear *ql, size_t m) {
     if (!ql || !ql->tmap_w8) return false;
     return m > 0 && m <= 0x7fffff00u;
@@ -418,7 +437,7 @@ int prefill_i8_prepare_layer(nne_qlinear *ql) {
     if (ql->n > 0x7fffff00u || ql->k > 0x7fffff00u) return NNE_OK;
     if ((reinterpret_cast<uintptr_t>(ql->q) & 15u) != 0) return NNE_OK;
     CUtensorMap *map = new CUtensorMap;
-    int st = tma_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ql->q, ql->k, ql->n, BKB, BN,
+    int st = tma_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ql->q, ql->k, ql->n, BKB, 256,
                              CU_TENSOR_MAP_SWIZZLE_128B);
     if (st != NNE_OK) {
         delete map;
@@ -438,8 +457,12 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
     nne_ctx *ctx = ql->ctx;
     static bool attr_set = false;
     if (!attr_set) {
-        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_i8_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_i8_kernel<256>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg<256>::SMEM_BYTES));
+        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_i8_kernel<128>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg<128>::SMEM_BYTES));
         attr_set = true;
     }
     // stream-ordered workspace: two int8 digit planes [m, k] and the per-row factors [m]
@@ -481,8 +504,16 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
         return st;
     }
     const int tiles_m = (int)((m + BM - 1) / BM);
-    const int tiles_n = (int)((ql->n + BN - 1) / BN);
-    const long long tiles = (long long)tiles_m * tiles_n;
+    // Tile width: rounds of tiles over the SMs, a 128-wide tile counted as 0.55 of a 256-wide one
+    // (half the MMAs, the same activation tiles to load).  The narrow tile wins where the wide one
+    // leaves SMs idle (m = 128: 43 tiles for 11008 channels) or its last round mostly empty.
+    const long long t256 = (long long)tiles_m * (long long)((ql->n + 255) / 256);
+    const long long t128 = (long long)tiles_m * (long long)((ql->n + 127) / 128);
+    const long long sms = ctx->sm_count;
+    const double cost256 = (double)((t256 + sms - 1) / sms);
+    const double cost128 = 0.55 * (double)((t128 + sms - 1) / sms);
+    const bool narrow = ql->tmap_wsk != nullptr && cost128 < cost256 && !prefill_wide_forced();
+    const long long tiles = narrow ? t128 : t256;
     if (tiles > 0x7fffffff) {
         cudaFreeAsync(ws, s);
         return fail(NNE_ERR_UNSUPPORTED, "too many output tiles");
@@ -492,14 +523,21 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)THREADS);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.dynamicSmemBytes = narrow ? Cfg<128>::SMEM_BYTES : Cfg<256>::SMEM_BYTES;
     cfg.stream = s;
     cfg.attrs = pdl;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(
-        &cfg, qlinear_prefill_i8_kernel, *static_cast<const CUtensorMap *>(ql->tmap_w8), tmap_x0,
-        tmap_x1, (const float *)unscale, (const float *)ql->scales, (const float *)ql->bias, y, (int)m,
-        (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
+    cudaError_t e;
+    if (narrow)  // the 128-row boxes are the small-batch kernel's tensor map of q
+        e = cudaLaunchKernelEx(&cfg, qlinear_prefill_i8_kernel<128>,
+                               *static_cast<const CUtensorMap *>(ql->tmap_wsk), tmap_x0, tmap_x1,
+                               (const float *)unscale, (const float *)ql->scales, (const float *)ql->bias,
+                               y, (int)m, (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
+    else
+        e = cudaLaunchKernelEx(&cfg, qlinear_prefill_i8_kernel<256>,
+                               *static_cast<const CUtensorMap *>(ql->tmap_w8), tmap_x0, tmap_x1,
+                               (const float *)unscale, (const float *)ql->scales, (const float *)ql->bias,
+                               y, (int)m, (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
     count_launch();
     cudaFreeAsync(ws, s);
     if (e != cudaSuccess)
