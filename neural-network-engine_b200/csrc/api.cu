@@ -207,7 +207,17 @@ int nne_cuda_ctx_create(int device, nne_ctx **out) {
     e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->absmax_word, 256);
     if (e == cudaSuccess) e = cudaMemset(ctx->absmax_word, 0, 256);
-    if (e == cudaSuccess) ctx->err_word = reinterpret_cast<int *>(ctx->absmax_word) + 16;
+    if (e == cudaSuccess) {
+        void *hp = nullptr;
+        e = cudaHostAlloc(&hp, 64, cudaHostAllocMapped);
+        if (e == cudaSuccess) {
+            ctx->err_host = static_cast<volatile int *>(hp);
+            *ctx->err_host = 0;
+            void *dp = nullptr;
+            e = cudaHostGetDevicePointer(&dp, hp, 0);
+            ctx->err_word = static_cast<int *>(dp);
+        }
+    }
     if (e == cudaSuccess) {
         // Keep freed stream-ordered workspaces cached in the pool instead of returning them to
         // the driver at every synchronisation.
@@ -240,6 +250,7 @@ int nne_cuda_ctx_destroy(nne_ctx *ctx) {
     ctx->stage_b.release();
     ctx->stage_c.release();
     if (ctx->absmax_word) cudaFree(ctx->absmax_word);
+    if (ctx->err_host) cudaFreeHost(const_cast<int *>(ctx->err_host));
     delete ctx;
     return NNE_OK;
     NNE_GUARD_END
@@ -249,10 +260,9 @@ int nne_cuda_ctx_check(nne_ctx *ctx) {
     NNE_GUARD_BEGIN
     NNE_TRY(use_ctx(ctx));
     NNE_CUDA_TRY(cudaDeviceSynchronize());
-    int word = 0;
-    NNE_CUDA_TRY(cudaMemcpy(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost));
+    const int word = *ctx->err_host;
     if (word != 0) {
-        NNE_CUDA_TRY(cudaMemset(ctx->err_word, 0, sizeof(int)));
+        *ctx->err_host = 0;
         return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
     }
     return NNE_OK;
@@ -606,11 +616,10 @@ int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, siz
     if (xb) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, x_host, xb, cudaMemcpyHostToDevice, s));
     NNE_TRY(forward_dev(ql, (const float *)ctx->stage_a.ptr, m, k, (float *)ctx->stage_b.ptr, ql->n, s));
     NNE_CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_b.ptr, yb, cudaMemcpyDeviceToHost, s));
-    int word = 0;
-    NNE_CUDA_TRY(cudaMemcpyAsync(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost, s));
     NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    const int word = *ctx->err_host;
     if (word != 0) {
-        cudaMemsetAsync(ctx->err_word, 0, sizeof(int), s);
+        *ctx->err_host = 0;
         return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
     }
     return NNE_OK;
@@ -737,11 +746,10 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
         off += len;
         i = j;
     }
-    int word = 0;
-    NNE_CUDA_TRY(cudaMemcpyAsync(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost, s));
     NNE_CUDA_TRY(cudaStreamSynchronize(s));
+    const int word = *ctx->err_host;
     if (word != 0) {
-        cudaMemsetAsync(ctx->err_word, 0, sizeof(int), s);
+        *ctx->err_host = 0;
         return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
     }
     return NNE_OK;

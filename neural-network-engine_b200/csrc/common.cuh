@@ -94,7 +94,8 @@ struct nne_ctx {
     std::mutex mu;                  // serialises *_host calls and workspace growth
     nne::GrowBuf stage_a, stage_b, stage_c;  // host-call staging (inputs / outputs)
     unsigned int *absmax_word = nullptr;     // 4-byte scratch for the per-tensor absmax
-    int *err_word = nullptr;                 // device error word: a kernel's bounded wait ran out
+    int *err_word = nullptr;                 // device address of the error word: a kernel's bounded wait ran out
+    volatile int *err_host = nullptr;        // the same word as the host sees it (mapped pinned memory)
 };
 
 struct nne_qlinear {

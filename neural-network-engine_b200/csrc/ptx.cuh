@@ -58,7 +58,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
                 *abort_flag = 1;
-                atomicCAS(err, 0, 0x100 + where);
+                // The context's error word lives in mapped host memory (the host reads it after a
+                // synchronise without a copy): a plain store, the last writer wins.
+                *reinterpret_cast<volatile int *>(err) = 0x100 + where;
+                __threadfence_system();
                 return false;
             }
         }
