@@ -115,7 +115,7 @@ struct alignas(64) SkLayer {
     const float *bias;
     float *y;
     size_t ldy;
-    long long *sums;       // [tiles][16][128] exact partial sums, zeroed by the pre-pass
+    long long *sums;       // [tiles][m][128] exact partial sums, zeroed by the pre-pass
     int *arrivals;         // [tiles][4] partial sums delivered so far per lane quarter, zeroed too
     const float *unscale;  // [16][2]: 2^-e of each row as two factors (NaN for a row with Inf/NaN)
     long long unit0;       // index of this layer's first (tile, k-block) unit in the launch
@@ -206,27 +206,38 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
             // tiles is requested before waiting for the pre-pass that writes the digit planes.
             int pre = 0;
             SkCur c;
+            // (tile, kb) of the current unit are carried along instead of divided out per unit: the
+            // producer is one thread, and its own instruction latency is what limits the ring.
+            int tile = 0, kb = 0;
             for (; pre < SK_STAGES && u0 + pre < u1; ++pre) {
                 const long long u = u0 + pre;
-                sk_seek(one, many, count, u, c);
-                const int lu = (int)(u - c.unit0);
-                const int tile = lu / c.num_kb, kb = lu % c.num_kb;
+                if (u >= c.end) {
+                    sk_seek(one, many, count, u, c);
+                    const int lu = (int)(u - c.unit0);
+                    tile = lu / c.num_kb;
+                    kb = lu % c.num_kb;
+                }
                 const uint32_t full = smem_u32(&bars->full[pre]);
                 mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
                 tma_load_2d_hint(smem_u32(smem + pre * SK_STAGE_BYTES), (many ? &many[c.li].tmap_w : &one.tmap_w), kb * SK_BKB,
                                  tile * SK_BM, full, pol_w);
+                if (++kb == c.num_kb) { kb = 0; ++tile; }
             }
             grid_dependency_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             c = SkCur();
+            const CUtensorMap *map_w = nullptr, *map_x = nullptr;
             for (long long u = u0; u < u1; ++u) {
-                sk_seek(one, many, count, u, c);
-                const CUtensorMap *map_w = many ? &many[c.li].tmap_w : &one.tmap_w;
-                const CUtensorMap *map_x = many ? &many[c.li].tmap_x : &one.tmap_x;
-                const int lu = (int)(u - c.unit0);
-                const int tile = lu / c.num_kb, kb = lu % c.num_kb;
+                if (u >= c.end) {
+                    sk_seek(one, many, count, u, c);
+                    map_w = many ? &many[c.li].tmap_w : &one.tmap_w;
+                    map_x = many ? &many[c.li].tmap_x : &one.tmap_x;
+                    const int lu = (int)(u - c.unit0);
+                    tile = lu / c.num_kb;
+                    kb = lu % c.num_kb;
+                }
                 uint8_t *st = smem + stage * SK_STAGE_BYTES;
                 const uint32_t full = smem_u32(&bars->full[stage]);
                 if (pre > 0) {
@@ -238,6 +249,7 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
                     tma_load_2d_hint(smem_u32(st), map_w, kb * SK_BKB, tile * SK_BM, full, pol_w);
                 }
                 tma_load_2d_hint(smem_u32(st + SK_W_BYTES), map_x, kb * SK_BKB, 0, full, pol_x);
+                if (++kb == c.num_kb) { kb = 0; ++tile; }
                 if (++stage == SK_STAGES) { stage = 0; phase ^= 1; }
             }
             if (!ok) {
@@ -313,7 +325,7 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
             // before the wait, so that only the TMEM read and the reduction follow the MMAs.
             const int ch = tile * SK_BM + ch_in_tile;
             const int n = SK_FIELD(n);
-            long long *dst = SK_FIELD(sums) + ((size_t)tile * SK_ROWS) * SK_BM + ch_in_tile;
+            long long *dst = SK_FIELD(sums) + ((size_t)tile * m) * SK_BM + ch_in_tile;
             int *ticket_word = SK_FIELD(arrivals) + tile * 4 + quarter;
             const float *bias = SK_FIELD(bias);
             const float *unscale = SK_FIELD(unscale);
@@ -539,7 +551,7 @@ int set_smem_attr() {
 
 size_t sk_tiles(size_t n) { return (n + SK_BM - 1) / SK_BM; }
 size_t sk_num_kb(size_t k) { return (k + SK_BKB - 1) / SK_BKB; }
-size_t sk_sums_bytes(size_t n) { return sk_tiles(n) * SK_ROWS * SK_BM * sizeof(long long); }
+size_t sk_sums_bytes(size_t n, size_t m) { return sk_tiles(n) * m * SK_BM * sizeof(long long); }
 size_t sk_arrivals_bytes(size_t n) { return (sk_tiles(n) * 4 * sizeof(int) + 255) & ~(size_t)255; }
 size_t sk_xd_bytes(size_t k) { return ((size_t)SK_N * k + 255) & ~(size_t)255; }
 
@@ -602,7 +614,7 @@ int launch_skinny(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ld
     nne_ctx *ctx = ql->ctx;
     const size_t k = ql->k, n = ql->n;
     // stream-ordered workspace: [sums | arrivals] (zeroed by the pre-pass), unscale, digit planes
-    const size_t sums_bytes = sk_sums_bytes(n);
+    const size_t sums_bytes = sk_sums_bytes(n, m);
     const size_t zero_bytes = sums_bytes + sk_arrivals_bytes(n);  // a multiple of 16
     const size_t uns_bytes = 256;
     uint8_t *ws = nullptr;
@@ -684,7 +696,7 @@ int skinny_plan_create(nne_ctx *ctx, nne_qlinear *const *layers, const float *co
     plan->in_count = (int)inputs.size();
     // one allocation: [sums and arrivals of every layer | unscale per input | digit planes per input]
     size_t zero_bytes = 0;
-    for (size_t i = 0; i < count; ++i) zero_bytes += sk_sums_bytes(layers[i]->n) + sk_arrivals_bytes(layers[i]->n);
+    for (size_t i = 0; i < count; ++i) zero_bytes += sk_sums_bytes(layers[i]->n, m) + sk_arrivals_bytes(layers[i]->n);
     size_t bytes = zero_bytes + 256 * inputs.size();
     for (const SkInput &in : inputs) bytes += sk_xd_bytes((size_t)in.k);
     NNE_CUDA_TRY(cudaMalloc(reinterpret_cast<void **>(&plan->ws), bytes));
@@ -719,7 +731,7 @@ int skinny_plan_create(nne_ctx *ctx, nne_qlinear *const *layers, const float *co
         L.tmap_x = xmaps[input_of[i]];
         L.unscale = inputs[input_of[i]].unscale;
         L.sums = reinterpret_cast<long long *>(z);
-        z += sk_sums_bytes(layers[i]->n);
+        z += sk_sums_bytes(layers[i]->n, m);
         L.arrivals = reinterpret_cast<int *>(z);
         z += sk_arrivals_bytes(layers[i]->n);
         L.unit0 = unit;
