@@ -18,7 +18,8 @@
 // One persistent CTA per SM walks 128 x 256 output tiles.  Per 128-wide k-block and stage:
 //   warp 0      TMA producer: int8 weight tile [256 x 128] and the two activation digit tiles
 //               [128 x 128], all 128B-swizzled straight into the UMMA K-major layout; no multicast
-//   warp 1      one thread issues 2 x 4 tcgen05.mma (128x256x32, kind::i8) and tcgen05.commit
+//   warp 1, 10  one thread each issues 4 tcgen05.mma (128x256x32, kind::i8) per k-block for one
+//               activation digit, and tcgen05.commit
 //   warps 2-9   epilogue: tcgen05.ld of both accumulators, combine, transpose through shared
 //               memory, scale, bias, coalesced f32 stores
 // Every mbarrier wait is bounded (~2 s): on expiry the context's device error word is set and the
@@ -51,7 +52,8 @@ struct Cfg {
     static constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                       ((uint32_t)(BM >> 4) << 24);
 };
-constexpr int THREADS = 32 * (2 + NUM_EPI_WARPS);
+constexpr int MMA_WARP_1 = 2 + NUM_EPI_WARPS;  // the second MMA issuer sits after the epilogue warps
+constexpr int THREADS = 32 * (3 + NUM_EPI_WARPS);
 
 __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -120,9 +122,9 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
-            mbar_init(smem_u32(&bars->empty[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 2);  // both MMA issuers commit
         }
-        mbar_init(smem_u32(&bars->acc_full), 1);
+        mbar_init(smem_u32(&bars->acc_full), 2);
         mbar_init(smem_u32(&bars->acc_empty), NUM_EPI_WARPS);
         bars->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -188,9 +190,16 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+    } else if (warp == 1 || warp == MMA_WARP_1) {
+        // ---------------- MMA issuers ----------------
+        // One warp per activation digit.  A single thread needs about as long to issue an MMA as
+        // the tensor pipe needs to run a 128 x 256 x 32 one, so with all eight MMAs of a k-block on
+        // one thread every barrier wait and descriptor update showed up as idle pipe; two issuers
+        // leave each with half the instructions.  Both commit to the stage's and the tile's
+        // barriers (count 2): tcgen05.commit covers the MMAs of the thread that executes it.
         if (lane == 0) {
+            const int digit = warp == 1 ? 0 : 1;
+            const uint32_t d_tmem = tmem_base + (uint32_t)(digit * BN);
             int stage = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
@@ -205,14 +214,12 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                     tc_fence_after();
                     uint8_t *st = smem + stage * STAGE_BYTES;
                     const uint64_t w_desc = make_kmajor_sw128_desc(smem_u32(st));
-                    const uint64_t x0_desc = make_kmajor_sw128_desc(smem_u32(st + W_BYTES));
-                    const uint64_t x1_desc = make_kmajor_sw128_desc(smem_u32(st + W_BYTES + X_BYTES));
+                    const uint64_t x_desc = make_kmajor_sw128_desc(smem_u32(st + W_BYTES + digit * X_BYTES));
 #pragma unroll
                     for (int kk = 0; kk < BKB / 32; ++kk) {
                         // +32 bytes per 32-element k step inside the 128-byte swizzle span
-                        const uint32_t accum = (kb | kk) != 0 ? 1u : 0u;
-                        umma_i8(tmem_base, x0_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), IDESC, accum);
-                        umma_i8(tmem_base + BN, x1_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), IDESC, accum);
+                        umma_i8(d_tmem, x_desc + (uint64_t)(kk * 2), w_desc + (uint64_t)(kk * 2), IDESC,
+                                (kb | kk) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&bars->empty[stage]));
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -417,11 +424,11 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
 
 }  // namespace
 
-// NNE_PREFILL_TILE=256 keeps the wide tile for every shape.
-static bool prefill_wide_forced() {
-    static const bool v = []() {
+// NNE_PREFILL_TILE=256 / =128 fixes the tile width for every shape (0: chosen per shape).
+static int prefill_tile_forced() {
+    static const int v = []() {
         const char *e = getenv("NNE_PREFILL_TILE");
-        return e && e[0] == '2';
+        return (e && e[0] == '2') ? 256 : (e && e[0] == '1') ? 128 : 0;
     }();
     return v;
 }
@@ -512,7 +519,8 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
     const long long sms = ctx->sm_count;
     const double cost256 = (double)((t256 + sms - 1) / sms);
     const double cost128 = 0.55 * (double)((t128 + sms - 1) / sms);
-    const bool narrow = ql->tmap_wsk != nullptr && cost128 < cost256 && !prefill_wide_forced();
+    const int forced = prefill_tile_forced();
+    const bool narrow = ql->tmap_wsk != nullptr && (forced ? forced == 128 : cost128 < cost256);
     const long long tiles = narrow ? t128 : t256;
     if (tiles > 0x7fffffff) {
         cudaFreeAsync(ws, s);
