@@ -443,6 +443,11 @@ def run_native(args):
     if world == 1:
         prefill = run_prefill(nne, lib, ctx, dev, make_layer, peaks, args)
 
+    # config 4: the 224 QLinears of a 7B-shaped decoder stack as independent forwards in one plan
+    stack = None
+    if world == 1:
+        stack = run_stack(nne, lib, ctx, dev, make_layer, peaks, args)
+
     out = None
     if rank == 0:
         cpu_v, cpu_cores, cpu_sample, _ = cpu_forward_rate(seconds_budget=8.0)
@@ -485,6 +490,8 @@ def run_native(args):
             out["decode_batch_sweep"] = sweep
         if prefill is not None:
             out["prefill"] = prefill
+        if stack is not None:
+            out["decoder_stack"] = stack
         print(json.dumps(out))
     for p in plans:
         lib.nne_qlinear_plan_destroy(p)
@@ -553,6 +560,51 @@ def run_decode_sweep(nne, lib, ctx, dev, layers, args):
     return {"cases": cases, "launch": "GB/s: one forward per layer, back to back (no plan, no graph); "
                                       "plan_GB/s: the 12 forwards as one plan",
             "kernels": {"1": "qgemv_stream_kernel", "4": "qlinear_skinny_i8_kernel"}}
+
+
+def run_stack(nne, lib, ctx, dev, make_layer, peaks, args):
+    """Config 4: 32 layers x {q, k, v, o: 4096->4096; gate, up: 4096->11008; down: 11008->4096} = 224
+    QLinears (6.5 GB of int8 codes), each fed its own N(0,1) activation of B rows, all 224 forwards
+    in one plan; tokens/s = B / device time."""
+    import torch
+    shapes = ([(4096, 4096)] * 4 + [(11008, 4096)] * 2 + [(4096, 11008)]) * 32
+    hs = [make_layer(n, k, 4000 + i) for i, (n, k) in enumerate(shapes)]
+    cnt = len(hs)
+    wbytes = sum(n * k for n, k in shapes)
+    stream = torch.cuda.current_stream()
+    cases = []
+    for b in (1, 8):
+        xs = [torch.randn(b, k, device=dev, dtype=torch.float32) for _, k in shapes]
+        ys = [torch.empty(b, n, device=dev, dtype=torch.float32) for n, _ in shapes]
+        plan = C.c_void_p()
+        if lib.nne_qlinear_plan_create(ctx.handle, cnt, (C.c_void_p * cnt)(*hs),
+                                       (C.c_void_p * cnt)(*[x.data_ptr() for x in xs]),
+                                       (C.c_void_p * cnt)(*[y.data_ptr() for y in ys]), b, C.byref(plan)) != 0:
+            raise RuntimeError(nne._lib.last_error())
+        for _ in range(3):
+            lib.nne_qlinear_plan_run(plan, stream.cuda_stream)
+        torch.cuda.synchronize()
+        iters = 10 if args.steps >= 10 else max(3, args.steps)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(iters):
+            if lib.nne_qlinear_plan_run(plan, stream.cuda_stream) != 0:
+                raise RuntimeError(nne._lib.last_error())
+        e1.record(stream)
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / iters
+        nbytes = sum(algorithmic_bytes(n, k, b) for n, k in shapes)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        cases.append({"batch": b, "ms": ms, "tokens_per_s": b / (ms * 1e-3), "GB/s": gbs,
+                      "frac_of_measured_hbm": gbs / peaks["hbm_gbs"],
+                      "launches": int(lib.nne_qlinear_plan_launches(plan))})
+        lib.nne_qlinear_plan_destroy(plan)
+        del xs, ys
+    for h in hs:
+        lib.nne_qlinear_destroy(h)
+    return {"layers": cnt, "weight_bytes": wbytes, "cases": cases,
+            "note": "224 independent forwards as one plan (batch 1: streaming GEMV; batch 8: small-batch "
+                    "tensor-core kernel)"}
 
 
 def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):

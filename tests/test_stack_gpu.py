@@ -143,6 +143,40 @@ def test_config4_decoder_stack(nne, ctx):
               f"{b / dt:.0f} tokens/s, {total_bytes / dt / 1e9:.0f} GB/s of weights")
         for p in plans:
             lib.nne_qlinear_plan_destroy(p)
+    # The 224 layers as INDEPENDENT forwards, each fed its own N(0,1) activation, all in one plan:
+    # tokens/s = batch / time of the 224 forwards.
+    flat = [(layer[name], n, k) for layer in stack for name, n, k in NAMES]
+    cnt = len(flat)
+    for b in (1, 8):
+        xs = [torch.randn(b, k, generator=gen, device=dev) for _, _, k in flat]
+        ys = [torch.empty(b, n, device=dev) for _, n, _ in flat]
+        p = C.c_void_p()
+        assert lib.nne_qlinear_plan_create(ctx.handle, cnt, (C.c_void_p * cnt)(*[h for h, _, _ in flat]),
+                                           (C.c_void_p * cnt)(*[x.data_ptr() for x in xs]),
+                                           (C.c_void_p * cnt)(*[y.data_ptr() for y in ys]), b,
+                                           C.byref(p)) == 0
+        assert lib.nne_qlinear_plan_launches(p) == (1 if b == 1 else 2)
+        for _ in range(2):
+            assert lib.nne_qlinear_plan_run(p, stream) == 0
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(5):
+            assert lib.nne_qlinear_plan_run(p, stream) == 0
+        e1.record()
+        torch.cuda.synchronize()
+        ctx.check()
+        dt = e0.elapsed_time(e1) * 1e-3 / 5
+        print(f"config4 batch {b}, 224 independent forwards as one plan: {dt * 1e3:.3f} ms, "
+              f"{b / dt:.0f} tokens/s, {total_bytes / dt / 1e9:.0f} GB/s of weights")
+        for i in (0, 3, 4, 6, 100, 223):   # one of every shape, first and last layer
+            h, n, k = flat[i]
+            y1 = torch.empty(b, n, device=dev)
+            fwd(h, xs[i], b, k, y1)
+            torch.cuda.synchronize()
+            assert torch.equal(y1.view(torch.int32), ys[i].view(torch.int32)), f"layer {i} differs"
+        lib.nne_qlinear_plan_destroy(p)
+        del xs, ys
     for layer in stack:
         for h in layer.values():
             lib.nne_qlinear_destroy(h)
