@@ -455,7 +455,9 @@ def run_native(args):
             "metric": "qlinear_int8_weight_stream_rate_m1", "value": value, "unit": "GB/s",
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+            "dtype_note": "int8 weights x int8 digit planes of the f32 activations -> exact int32/int64 "
+                          "sums (dp4a), one rounding to f32, f32 scale and bias",
             "config": {"workload": "config2-decode-7B-projections-M1", "shapes_NK": SHAPES,
                        "m": 1, "replicas_per_shape": REPLICAS, "layers_per_step": len(layers),
                        "weight_bytes_per_step_per_gpu": sum(L["n"] * L["k"] for L in layers),
