@@ -13,6 +13,7 @@
 //
 // HBM traffic per row-quantize launch: 4*rows*cols read + rows*cols + 4*rows written.
 #include "common.cuh"
+#include "ptx.cuh"
 
 namespace nne {
 namespace {
@@ -116,6 +117,89 @@ quantize_rows_cta_kernel(const float *__restrict__ w, size_t rows, size_t cols,
     }
 }
 
+// The same row loop with the row brought into shared memory by a 1-D bulk copy, two rows per CTA
+// in flight: while a row is reduced and coded out of one buffer the next one is already on its
+// way into the other, so the CTA always has loads outstanding (the kernel above has none while it
+// computes).  Needs cols % 4 == 0, a 16-byte aligned base and a row of at most 64 KB.
+__global__ void __launch_bounds__(256)
+quantize_rows_bulk_kernel(const float *__restrict__ w, size_t rows, size_t cols,
+                          int8_t *__restrict__ q, float *__restrict__ scales, int *err) {
+    extern __shared__ __align__(128) uint8_t qsmem[];
+    __shared__ uint64_t full[2];
+    __shared__ float warp_part[8];
+    __shared__ float row_max;
+    __shared__ int abort_word;
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const uint32_t row_bytes = (uint32_t)(cols * sizeof(float));
+    const size_t n4 = cols >> 2;
+    volatile int *abort_flag = &abort_word;
+    if (tid == 0) {
+        mbar_init(smem_u32(&full[0]), 1);
+        mbar_init(smem_u32(&full[1]), 1);
+        abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const uint64_t pol = l2_policy_evict_first();
+        for (int b = 0; b < 2; ++b) {
+            const size_t row = (size_t)blockIdx.x + (size_t)b * gridDim.x;
+            if (row < rows) {
+                mbar_arrive_expect_tx(smem_u32(&full[b]), row_bytes);
+                bulk_load_1d_hint(smem_u32(qsmem + (size_t)b * row_bytes), w + row * cols, row_bytes,
+                                  smem_u32(&full[b]), pol);
+            }
+        }
+    }
+    __syncthreads();
+    size_t it = 0;
+    for (size_t row = blockIdx.x; row < rows; row += gridDim.x, ++it) {
+        const int b = (int)(it & 1);
+        if (!mbar_wait(smem_u32(&full[b]), (uint32_t)((it >> 1) & 1), abort_flag, err, 0x41)) break;
+        const float4 *cache4 = reinterpret_cast<const float4 *>(qsmem + (size_t)b * row_bytes);
+        float m = 0.0f;
+        for (size_t i = tid; i < n4; i += 256) {
+            const float4 v = cache4[i];
+            m = absmax_acc(absmax_acc(absmax_acc(absmax_acc(m, v.x), v.y), v.z), v.w);
+        }
+        m = warp_max(m);
+        if (lane == 0) warp_part[wid] = m;
+        __syncthreads();
+        if (wid == 0) {
+            float t = (lane < 8) ? warp_part[lane] : 0.0f;
+            t = warp_max(t);
+            if (lane == 0) {
+                row_max = t;
+                scales[row] = scale_from_max(t);
+            }
+        }
+        __syncthreads();
+        const float inv = __fdiv_rn(1.0f, scale_from_max(row_max));
+        uint32_t *dst4 = reinterpret_cast<uint32_t *>(q + row * cols);
+        for (size_t i = tid; i < n4; i += 256) {
+            const float4 v = cache4[i];
+            dst4[i] = pack4(quant_code(v.x, inv), quant_code(v.y, inv), quant_code(v.z, inv),
+                            quant_code(v.w, inv));
+        }
+        __syncthreads();  // every thread is done with buffer b, warp_part and row_max
+        if (tid == 0) {
+            const size_t next = row + 2 * (size_t)gridDim.x;
+            if (next < rows) {
+                fence_proxy_async();  // the generic-proxy reads above come before the async write
+                mbar_arrive_expect_tx(smem_u32(&full[b]), row_bytes);
+                bulk_load_1d_hint(smem_u32(qsmem + (size_t)b * row_bytes), w + next * cols, row_bytes,
+                                  smem_u32(&full[b]), l2_policy_evict_first());
+            }
+        }
+    }
+    // A wait that ran out leaves copies in flight: let them land before the CTA exits.
+    if (*abort_flag && tid == 0) {
+        for (int b = 0; b < 2; ++b) {
+            const unsigned long long t0 = globaltimer_ns();
+            while (!mbar_try_wait(smem_u32(&full[b]), 0) && !mbar_try_wait(smem_u32(&full[b]), 1) &&
+                   globaltimer_ns() - t0 < 100000000ull) {
+            }
+        }
+    }
+}
+
 // One warp per row, for short rows (cols <= 1024): the second pass re-reads the row, which is
 // at most 4 KB and still in L1.  Many short rows (e.g. 64 -> 128 layers) stay efficient.
 __global__ void __launch_bounds__(256)
@@ -203,6 +287,15 @@ dequantize_rows_kernel(const int8_t *__restrict__ q, const float *__restrict__ s
 
 }  // namespace
 
+// NNE_QUANT_BULK=0 keeps the register-staged row kernel.
+static bool quantize_bulk_disabled() {
+    static const bool v = []() {
+        const char *e = getenv("NNE_QUANT_BULK");
+        return e && e[0] == '0';
+    }();
+    return v;
+}
+
 int launch_quantize_rows(nne_ctx *ctx, const float *w, size_t rows, size_t cols, int8_t *q,
                          float *scales, cudaStream_t s) {
     if (rows == 0) return NNE_OK;
@@ -223,6 +316,21 @@ int launch_quantize_rows(nne_ctx *ctx, const float *w, size_t rows, size_t cols,
     }
     const bool vec = (cols % 4 == 0) && ((reinterpret_cast<uintptr_t>(w) & 15u) == 0) &&
                      ((reinterpret_cast<uintptr_t>(q) & 3u) == 0);
+    if (vec && cols * sizeof(float) <= 64 * 1024 && !quantize_bulk_disabled()) {
+        // two row buffers per CTA; as many CTAs per SM as 200 KB of shared memory hold (at most 6)
+        const size_t smem2 = 2 * cols * sizeof(float);
+        size_t per = (200 * 1024) / smem2;
+        if (per > 6) per = 6;
+        if (per < 1) per = 1;
+        size_t nblocks = rows;
+        if (nblocks > (size_t)ctx->sm_count * per) nblocks = (size_t)ctx->sm_count * per;
+        NNE_CUDA_TRY(cudaFuncSetAttribute(quantize_rows_bulk_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+        quantize_rows_bulk_kernel<<<(unsigned)nblocks, 256, smem2, s>>>(w, rows, cols, q, scales,
+                                                                       ctx->err_word);
+        NNE_LAUNCH_CHECK();
+        return NNE_OK;
+    }
     // Shared row cache: the whole row when it fits in 64 KB (3 CTAs/SM), else the first 64 KB.
     size_t cache_floats = cols < 16384 ? cols : 16384;
     cache_floats &= ~(size_t)3;
