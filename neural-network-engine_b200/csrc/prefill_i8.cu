@@ -422,7 +422,127 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
     }
 }
 
+// The same pre-pass with the row brought into shared memory by a 1-D bulk copy, two row buffers
+// per CTA: while a row is scanned and turned into digits the next one is already on its way, so
+// the CTA always has a load outstanding.  For rows of at most 64 KB (k <= 16384).
+__global__ void __launch_bounds__(256)
+x_to_digits_bulk_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t *__restrict__ x1,
+                        float *__restrict__ unscale, int m, int k, int *err) {
+    extern __shared__ __align__(128) uint8_t xsmem[];
+    __shared__ uint64_t full[2];
+    __shared__ float wmax[8];
+    __shared__ int wbad[8];
+    __shared__ int abort_word;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n4 = k >> 2;
+    const uint32_t row_bytes = (uint32_t)k * 4u;
+    volatile int *abort_flag = &abort_word;
+    if (tid == 0) {
+        mbar_init(smem_u32(&full[0]), 1);
+        mbar_init(smem_u32(&full[1]), 1);
+        abort_word = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // x may be the output of the previous kernel in the stream, and the digit planes may still
+    // be read by it: nothing is touched before that kernel has finished.
+    grid_dependency_wait();
+    grid_launch_dependents();
+    if (tid == 0) {
+        for (int b = 0; b < 2; ++b) {
+            const long long row = (long long)blockIdx.x + (long long)b * gridDim.x;
+            if (row < m) {
+                mbar_arrive_expect_tx(smem_u32(&full[b]), row_bytes);
+                bulk_load_1d(smem_u32(xsmem + (size_t)b * row_bytes), x + (size_t)row * k, row_bytes,
+                             smem_u32(&full[b]));
+            }
+        }
+    }
+    __syncthreads();
+    int it = 0;
+    for (int row = blockIdx.x; row < m; row += gridDim.x, ++it) {
+        const int b = it & 1;
+        if (!mbar_wait(smem_u32(&full[b]), (uint32_t)((it >> 1) & 1), abort_flag, err, 0x26)) break;
+        const float4 *src = reinterpret_cast<const float4 *>(xsmem + (size_t)b * row_bytes);
+        float mx = 0.0f;
+        int bad = 0;
+        for (int i = tid; i < n4; i += 256) {
+            const float4 t = src[i];
+            const float a0 = fabsf(t.x), a1 = fabsf(t.y), a2 = fabsf(t.z), a3 = fabsf(t.w);
+            bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) | !(a2 <= 3.402823466e38f) |
+                   !(a3 <= 3.402823466e38f);
+            mx = fmaxf(fmaxf(mx, fmaxf(a0, a1)), fmaxf(a2, a3));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        bad = __any_sync(0xffffffffu, bad);
+        if (lane == 0) {
+            wmax[warp] = mx;
+            wbad[warp] = bad;
+        }
+        __syncthreads();
+        mx = 0.0f;
+        bad = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            mx = fmaxf(mx, wmax[w]);
+            bad |= wbad[w];
+        }
+        const int e = 12 - ((mx > 0.0f) ? ilogbf(mx) : 0);
+        const int e1 = e >> 1, e2 = e - e1;  // 2^e = 2^e1 * 2^e2, both factors finite
+        const float f1 = __int_as_float((127 + e1) << 23), f2 = __int_as_float((127 + e2) << 23);
+        if (tid == 0) {
+            const float u = __int_as_float((127 - e1) << 23) * __int_as_float((127 - e2) << 23);
+            unscale[row] = bad ? __int_as_float(0x7fc00000) : u;
+        }
+        uint32_t *d0p = reinterpret_cast<uint32_t *>(x0 + (size_t)row * k);
+        uint32_t *d1p = reinterpret_cast<uint32_t *>(x1 + (size_t)row * k);
+        for (int i = tid; i < n4; i += 256) {
+            const float4 t = src[i];
+            const float xv[4] = {t.x, t.y, t.z, t.w};
+            uint32_t w0 = 0u, w1 = 0u;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int v = bad ? 0 : __float2int_rn(xv[c] * f1 * f2);
+                const int d0 = ((v + 64) & 127) - 64;
+                const int d1 = (v - d0) >> 7;
+                w0 |= (uint32_t)(d0 & 0xff) << (8 * c);
+                w1 |= (uint32_t)(d1 & 0xff) << (8 * c);
+            }
+            d0p[i] = w0;
+            d1p[i] = w1;
+        }
+        __syncthreads();  // every thread is done with buffer b, wmax and wbad
+        if (tid == 0) {
+            const long long next = (long long)row + 2ll * gridDim.x;
+            if (next < m) {
+                fence_proxy_async();  // the generic-proxy reads above come before the async write
+                mbar_arrive_expect_tx(smem_u32(&full[b]), row_bytes);
+                bulk_load_1d(smem_u32(xsmem + (size_t)b * row_bytes), x + (size_t)next * k, row_bytes,
+                             smem_u32(&full[b]));
+            }
+        }
+    }
+    // A wait that ran out leaves copies in flight: let them land before the CTA exits.
+    if (*abort_flag && tid == 0) {
+        for (int b = 0; b < 2; ++b) {
+            const unsigned long long t0 = globaltimer_ns();
+            while (!mbar_try_wait(smem_u32(&full[b]), 0) && !mbar_try_wait(smem_u32(&full[b]), 1) &&
+                   globaltimer_ns() - t0 < 100000000ull) {
+            }
+        }
+    }
+}
+
 }  // namespace
+
+// NNE_PREPASS_BULK=0 keeps the register-staged activation pre-pass.
+static bool prepass_bulk_disabled() {
+    static const bool v = []() {
+        const char *e = getenv("NNE_PREPASS_BULK");
+        return e && e[0] == '0';
+    }();
+    return v;
+}
 
 // NNE_PREFILL_TILE=256 / =128 fixes the tile width for every shape (0: chosen per shape).
 static int prefill_tile_forced() {
@@ -488,12 +608,31 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
         const size_t cap = (size_t)ctx->sm_count * 32;
         if (blocks > cap) blocks = cap;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)blocks);
         cfg.blockDim = dim3(256);
         cfg.stream = s;
         cfg.attrs = pdl;
         cfg.numAttrs = pdl_enabled() ? 1 : 0;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, x_to_digits_kernel, x, x0, x1, unscale, (int)m, (int)ql->k);
+        cudaError_t e;
+        const size_t smem2 = 2 * ql->k * sizeof(float);
+        if (smem2 <= 128 * 1024 && !prepass_bulk_disabled()) {
+            static bool xattr = false;
+            if (!xattr) {
+                cudaFuncSetAttribute(x_to_digits_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     128 * 1024);
+                xattr = true;
+            }
+            size_t per = (200 * 1024) / smem2;
+            if (per > 6) per = 6;
+            size_t nb = m;
+            if (nb > (size_t)ctx->sm_count * per) nb = (size_t)ctx->sm_count * per;
+            cfg.gridDim = dim3((unsigned)nb);
+            cfg.dynamicSmemBytes = smem2;
+            e = cudaLaunchKernelEx(&cfg, x_to_digits_bulk_kernel, x, x0, x1, unscale, (int)m, (int)ql->k,
+                                   ctx->err_word);
+        } else {
+            cfg.gridDim = dim3((unsigned)blocks);
+            e = cudaLaunchKernelEx(&cfg, x_to_digits_kernel, x, x0, x1, unscale, (int)m, (int)ql->k);
+        }
         count_launch();
         if (e != cudaSuccess) {
             cudaFreeAsync(ws, s);
