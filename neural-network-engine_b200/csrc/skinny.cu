@@ -25,6 +25,11 @@
 // The pre-pass kernel (digits of x, per-row 2^-e, zeroing of the workspace) runs just before and
 // the two are chained with programmatic dependent launch: the weight ring fills while the
 // pre-pass runs.
+//
+// The kernel is driven by per-layer descriptors (SkLayer).  A single forward passes one in the
+// parameter block; a plan (nne_qlinear_plan_*, 2 <= m <= 16) keeps an array of them in device
+// memory and runs all its layers as ONE pre-pass + ONE launch over the concatenated units, with
+// layers that read the same x sharing one set of digit planes.
 #include <memory>
 #include <vector>
 
