@@ -150,3 +150,30 @@ def test_small_batch_plan_many_layers_big_shapes(nne, ctx):
     ctx.check()
     for (ql, x, b), y in zip(refs, ys):
         assert np.array_equal(y.cpu().numpy().view(np.uint32), ql.forward(x).view(np.uint32))
+
+
+def test_reserved_sms_leave_results_unchanged(nne, ctx):
+    """nne_cuda_ctx_reserve_sms shrinks the streaming kernel's grid; row ranges per CTA change,
+    results must not (each output channel is one exact integer sum)."""
+    import torch
+    lib = nne.load()
+    own = nne.CudaContext(0)  # a context of its own: the setting must not leak into other tests
+    shapes = [(1000, 512, True), (4096, 4096, False), (300, 2048, True)]
+    layers, xs, ys, refs = build(nne, own, shapes, 1, 141)
+    plan = nne.QLinearPlan(layers, [t.data_ptr() for t in xs], [t.data_ptr() for t in ys], 1, own)
+    s = torch.cuda.current_stream().cuda_stream
+    plan.run(s)
+    torch.cuda.synchronize()
+    base = [y.clone() for y in ys]
+    for reserve in (8, 100, 147, 0):
+        assert lib.nne_cuda_ctx_reserve_sms(own.handle, reserve) == 0
+        for y in ys:
+            y.fill_(float("nan"))
+        plan.run(s)
+        torch.cuda.synchronize()
+        own.check()
+        for y, b in zip(ys, base):
+            assert torch.equal(y.view(torch.int32), b.view(torch.int32)), f"reserve={reserve}"
+    assert lib.nne_cuda_ctx_reserve_sms(own.handle, -1) != 0
+    assert lib.nne_cuda_ctx_reserve_sms(own.handle, 100000) != 0
+    plan.close()
