@@ -196,6 +196,42 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # native arm
 # ---------------------------------------------------------------------------------------------
+class RawNccl:
+    """ncclAllGather called straight through ctypes on the NCCL library torch has loaded, with a
+    communicator of its own (unique id broadcast over torch.distributed).  The c10d wrapper costs
+    tens of microseconds of host time per call - more than is left per 73 us step once eight ranks
+    share the host's cores; the direct call costs a few."""
+
+    def __init__(self, torch, dist, rank, world, dev):
+        path = os.path.join(os.path.dirname(torch.__file__), "..", "nvidia", "nccl", "lib", "libnccl.so.2")
+        self.lib = C.CDLL(path if os.path.exists(path) else "libnccl.so.2")
+
+        class UniqueId(C.Structure):
+            _fields_ = [("internal", C.c_byte * 128)]
+
+        uid = UniqueId()
+        if rank == 0 and self.lib.ncclGetUniqueId(C.byref(uid)) != 0:
+            raise RuntimeError("ncclGetUniqueId failed")
+        t = torch.tensor(list(bytes(uid)), dtype=torch.uint8, device=dev)
+        dist.broadcast(t, 0)
+        C.memmove(C.byref(uid), bytes(t.cpu().tolist()), 128)
+        self.lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
+        self.lib.ncclAllGather.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p]
+        self.comm = C.c_void_p()
+        if self.lib.ncclCommInitRank(C.byref(self.comm), world, uid, rank) != 0:
+            raise RuntimeError("ncclCommInitRank failed")
+
+    def all_gather_f32(self, send_ptr, recv_ptr, count, stream_ptr):
+        if self.lib.ncclAllGather(send_ptr, recv_ptr, count, 7, self.comm, stream_ptr) != 0:  # 7 = ncclFloat32
+            raise RuntimeError("ncclAllGather failed")
+
+    def close(self):
+        if self.comm:
+            self.lib.ncclCommDestroy.argtypes = [C.c_void_p]
+            self.lib.ncclCommDestroy(self.comm)
+            self.comm = C.c_void_p()
+
+
 def run_native(args):
     import numpy as np
     import torch
@@ -210,6 +246,10 @@ def run_native(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # The all-gather runs beside the next step's kernel on the SMs that kernel leaves free
+        # (RESERVED_SMS): cap the collective's CTAs at that number, or it waits for the kernel to
+        # end (measured at N = 8 without the cap: 102.8 us per step against 72.7 on one GPU).
+        os.environ.setdefault("NCCL_MAX_CTAS", str(RESERVED_SMS))
         dist.init_process_group("nccl", device_id=dev)
 
     nne = importlib.import_module("neural-network-engine_b200")
@@ -271,6 +311,20 @@ def run_native(args):
         if lib.nne_cuda_ctx_reserve_sms(ctx.handle, RESERVED_SMS) != 0:
             raise RuntimeError(nne._lib.last_error())
     comm = torch.cuda.Stream() if overlap else None
+    raw = None
+    if overlap:
+        # every rank must take the same route: agree on whether the direct communicator came up
+        try:
+            raw = RawNccl(torch, dist, rank, world, dev)
+            good = 1
+        except Exception:
+            raw, good = None, 0
+        flag = torch.tensor([good], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            if raw is not None:
+                raw.close()
+            raw = None
     plan_done = [torch.cuda.Event() for _ in range(nslabs)]
     gather_done = [torch.cuda.Event() for _ in range(nslabs)]
     step_no = [0]
@@ -284,10 +338,13 @@ def run_native(args):
             raise RuntimeError(nne._lib.last_error())
         if overlap:
             plan_done[sl].record(stream)
-            with torch.cuda.stream(comm):
-                comm.wait_event(plan_done[sl])
-                dist.all_gather_into_tensor(gathered[sl].view(-1), own[sl])
-                gather_done[sl].record(comm)
+            comm.wait_event(plan_done[sl])
+            if raw is not None:  # in place: this rank's slice already sits in its slot
+                raw.all_gather_f32(own[sl].data_ptr(), gathered[sl].data_ptr(), slab_len, comm.cuda_stream)
+            else:
+                with torch.cuda.stream(comm):
+                    dist.all_gather_into_tensor(gathered[sl].view(-1), own[sl])
+            gather_done[sl].record(comm)
         elif world > 1:
             dist.all_gather_into_tensor(gathered[0].view(-1), own[0])
 
@@ -322,8 +379,10 @@ def run_native(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(stream)
+    h0 = time.perf_counter()
     for _ in range(args.steps):
         step()
+    host_us_per_step = (time.perf_counter() - h0) * 1e6 / args.steps  # enqueue only, nothing waited for
     drain()
     e1.record(stream)
     barrier()
@@ -484,6 +543,9 @@ def run_native(args):
                                   "api": "nne_qlinear_forward_host, 12 calls per step (per call H2D + "
                                          "launch + D2H + sync)"}},
             "gpu_launches": int(launches),
+            "host_enqueue_us_per_step": host_us_per_step,
+            "collective": None if world == 1 else ("ncclAllGather called directly (ctypes)" if raw is not None
+                                                    else "torch.distributed all_gather_into_tensor"),
             "clocks": clocks,
         }
         if per_layer is not None:
@@ -495,6 +557,9 @@ def run_native(args):
         if stack is not None:
             out["decoder_stack"] = stack
         print(json.dumps(out))
+    if raw is not None:
+        torch.cuda.synchronize()
+        raw.close()
     for p in plans:
         lib.nne_qlinear_plan_destroy(p)
     for L in layers:
