@@ -66,6 +66,10 @@ NNE_API int nne_last_error(char *buf, size_t n);
 /* ---- context ------------------------------------------------------------------------------
  * Plays the role of Arc<GpuContext> of the existing device backend (src/gpu/context.rs:20-59,
  * src/gpu/layers.rs:12-16): created once, shared by every layer placed on that device.       */
+/* Side effect on the process: creation raises the release threshold of the device's DEFAULT
+ * stream-ordered memory pool to "keep everything" (cudaMemPoolAttrReleaseThreshold), so that the
+ * forwards' stream-ordered workspaces are reused instead of returned to the driver at every
+ * synchronisation.  A host application that shares that pool inherits the setting. */
 NNE_API int nne_cuda_ctx_create(int device, nne_ctx **out);
 NNE_API int nne_cuda_ctx_destroy(nne_ctx *ctx);
 /* Synchronises the device and reads the context's device error word.  Kernels here never spin
@@ -154,9 +158,14 @@ NNE_API int nne_qlinear_forward_dev_strided(nne_qlinear *ql, const float *x_dev,
  * may not allocate device memory while they run - a serving loop whose memory budget was handed
  * out in full at start-up, or a thread that issues work while a collective is in flight and
  * cannot risk the device-wide synchronisation an allocation can bring.  Same contraction as
- * nne_qlinear_forward_dev, within the same tolerance: it always runs the bf16 tensor-core kernel
- * (codes dequantized to bf16 in shared memory, activations rounded to bf16), whose bf16 copy of
- * the activations lives here in a fixed 8 MiB array in the library's device image
+ * nne_qlinear_forward_dev, but with a LOOSER error bound: it always runs the bf16 tensor-core
+ * kernel (codes dequantized to bf16 in shared memory - exact - and activations rounded to bf16,
+ * fp32 accumulation), so per output channel j
+ *     |y - exact| <= 2^-8 * ||x||inf * scale_j * sum_k |q_jk|   (+ fp32 summation error),
+ * i.e. up to 3.9 times the 1e-3 tolerance nne_qlinear_forward_dev keeps; on N(0,1)
+ * activations the rounding errors average out to a few percent of that tolerance, and on
+ * activations that are exact in bf16 the result equals nne_qlinear_forward_dev's bit for bit.
+ * The bf16 copy of the activations lives in a fixed 8 MiB array in the library's device image
  * (every GPU that loads the library holds it until the process exits) instead of a stream-ordered
  * allocation.  Limits: in_features % 16 == 0, x_dev 16-byte aligned, and m * in_features <=
  * 4 194 304 (4 Mi elements); anything larger is refused with NNE_ERR_INVALID_ARGUMENT and a

@@ -6,8 +6,10 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <map>
 #include <memory>
 #include <new>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -29,6 +31,17 @@ int fail(int status, const char *fmt, ...) {
     va_end(ap);
     last_error_ref() = buf;
     return status;
+}
+
+int ensure_dynamic_smem(int device, const void *func, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<int, const void *>, size_t> have;
+    std::lock_guard<std::mutex> lock(mu);
+    size_t &cur = have[std::make_pair(device, func)];
+    if (bytes <= cur) return NNE_OK;
+    NNE_CUDA_TRY(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    cur = bytes;
+    return NNE_OK;
 }
 
 int GrowBuf::reserve(size_t bytes) {
@@ -111,7 +124,11 @@ int pick_kernel(const nne_qlinear *ql, size_t m, const float *x, const float *y)
     const bool base_ok = aligned(ql->q, 16) && (x == nullptr || aligned(x, 16)) &&
                          (y == nullptr || aligned(y, 4));
     if (base_ok && skinny_supports(ql, m) && !skinny_disabled()) return 4;
-    if (m > 16 && base_ok && (prefill_i8_supports(ql, m) || prefill_supports(ql, m))) return 2;
+    // The bf16 tensor-core kernel rounds x to bf16 (worst case above the path's tolerance), so it
+    // runs only when asked for; a shape the integer kernel declines goes to the fp32 kernels.
+    if (m > 16 && base_ok &&
+        (prefill_bf16_forced() ? prefill_supports(ql, m) : prefill_i8_supports(ql, m)))
+        return 2;
     if (base_ok && gemv_supports(ql->n, ql->k, m)) return 1;
     return 3;
 }
@@ -134,7 +151,7 @@ int forward_dev(nne_qlinear *ql, const float *x, size_t m, size_t k, float *y, s
     }
     switch (pick_kernel(ql, m, x, y)) {
         case 2:
-            if (prefill_i8_supports(ql, m) && !prefill_bf16_forced()) return launch_prefill_i8(ql, x, y, m, ldy, s);
+            if (!prefill_bf16_forced()) return launch_prefill_i8(ql, x, y, m, ldy, s);
             return launch_prefill(ql, x, y, m, ldy, s);
         case 4:
             return launch_skinny(ql, x, y, m, ldy, s);

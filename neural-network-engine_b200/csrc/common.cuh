@@ -49,6 +49,10 @@ int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)))
         return ::nne::fail(NNE_ERR_INVALID_ARGUMENT, "unknown exception");         \
     }
 
+// Longest row the integer tensor-core kernels take: |q| <= 128 times a digit |d| <= 64 is 2^13, and
+// an int32 accumulator in TMEM adds in_features of those, so sums stay exact up to 2^18 terms.
+constexpr size_t NNE_TENSOR_INT_MAX_K = (size_t)1 << 18;
+
 // ---- launch counter ----------------------------------------------------------------------
 extern std::atomic<uint64_t> g_launches;
 // Programmatic dependent launch is on unless NNE_PDL=0.
@@ -71,6 +75,15 @@ inline void count_launch(int n = 1) { g_launches.fetch_add((uint64_t)n, std::mem
             return ::nne::fail(NNE_ERR_CUDA, "kernel launch failed: %s (%s:%d)",         \
                                cudaGetErrorString(e__), __FILE__, __LINE__);             \
     } while (0)
+
+// Raises a kernel's MaxDynamicSharedMemorySize to at least `bytes` on `device` (the attribute is
+// per device, so it is tracked per (device, kernel) and only ever raised; safe from any thread).
+// The device must be the calling thread's current one.
+int ensure_dynamic_smem(int device, const void *func, size_t bytes);
+template <typename K>
+inline int ensure_dynamic_smem(int device, K *kernel, size_t bytes) {
+    return ensure_dynamic_smem(device, reinterpret_cast<const void *>(kernel), bytes);
+}
 
 // A device buffer that only ever grows; used for host-call staging and kernel workspaces.
 struct GrowBuf {

@@ -197,7 +197,7 @@ __device__ __noinline__ void consume_stage_fp32(const StreamLayer &L, const uint
                 for (int m = 0; m < MT; ++m) {
                     const float *xr = L.x + (size_t)m * k + (size_t)c * 16;
 #pragma unroll
-                    for (int v = 0; v < 16; ++v) facc[m] = fmaf(__ldg(xr + v), wf[v], facc[m]);
+                    for (int v = 0; v < 16; ++v) facc[m] = fmaf(xr[v], wf[v], facc[m]);
                 }
             }
         }
@@ -338,7 +338,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                     const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
-                        const float4 t4 = ldg_f4_hint(p4 + v, pol_keep);
+                        const float4 t4 = ld_f4_hint(p4 + v, pol_keep);
                         const float a0 = fabsf(t4.x), a1 = fabsf(t4.y), a2 = fabsf(t4.z), a3 = fabsf(t4.w);
                         bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) |
                                !(a2 <= 3.402823466e38f) | !(a3 <= 3.402823466e38f);
@@ -394,7 +394,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                             float xv[16];
 #pragma unroll
                             for (int v = 0; v < 4; ++v) {
-                                const float4 t4 = __ldg(p4 + v);
+                                const float4 t4 = p4[v];
                                 xv[4 * v + 0] = t4.x;
                                 xv[4 * v + 1] = t4.y;
                                 xv[4 * v + 2] = t4.z;
@@ -472,12 +472,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
 template <int MT>
 int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot_bytes, int kpad,
                      int sb_rows, int bufs, size_t smem, int grid, cudaStream_t s) {
-    static size_t attr_smem = 0;
-    if (smem > attr_smem) {
-        NNE_CUDA_TRY(cudaFuncSetAttribute(qgemv_stream_kernel<MT>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        attr_smem = smem;
-    }
+    NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_kernel<MT>, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)THREADS);

@@ -249,7 +249,8 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
             const int m0 = (t % tiles_m) * BM, n0 = (t / tiles_m) * BN;
             const int row0 = m0 + quarter * 32;
             const int row = row0 + lane;
-            const float us = (row < m) ? __ldg(unscale + row) : 0.0f;
+            // written by the pre-pass while this kernel may already be resident: a coherent load
+            const float us = (row < m) ? __ldcg(unscale + row) : 0.0f;
             ok = mbar_wait(smem_u32(&bars->acc_full), acc_phase, abort_flag, err, 0x24);
             if (!ok) break;
             tc_fence_after();
@@ -561,7 +562,8 @@ bool prefill_i8_supports(const nne_qlinear *ql, size_t m) {
 int prefill_i8_prepare_layer(nne_qlinear *ql) {
     ql->tmap_w8 = nullptr;
     if (ql->n == 0 || ql->k == 0 || ql->k % 16 != 0) return NNE_OK;
-    if (ql->n > 0x7fffff00u || ql->k > 0x7fffff00u) return NNE_OK;
+    // int32 accumulators in TMEM: exact only up to 2^18 terms of at most 2^13 each
+    if (ql->n > 0x7fffff00u || ql->k > NNE_TENSOR_INT_MAX_K) return NNE_OK;
     if ((reinterpret_cast<uintptr_t>(ql->q) & 15u) != 0) return NNE_OK;
     CUtensorMap *map = new CUtensorMap;
     int st = tma_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ql->q, ql->k, ql->n, BKB, 256,
@@ -582,16 +584,8 @@ void prefill_i8_release_layer(nne_qlinear *ql) {
 int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
                       cudaStream_t s) {
     nne_ctx *ctx = ql->ctx;
-    static bool attr_set = false;
-    if (!attr_set) {
-        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_i8_kernel<256>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg<256>::SMEM_BYTES));
-        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_prefill_i8_kernel<128>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg<128>::SMEM_BYTES));
-        attr_set = true;
-    }
+    NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<256>, Cfg<256>::SMEM_BYTES));
+    NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<128>, Cfg<128>::SMEM_BYTES));
     // stream-ordered workspace: two int8 digit planes [m, k] and the per-row factors [m]
     const size_t plane = m * ql->k;
     const size_t bytes = 2 * plane + ((m * sizeof(float) + 255) & ~(size_t)255) + 256;
@@ -615,12 +609,7 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
         cudaError_t e;
         const size_t smem2 = 2 * ql->k * sizeof(float);
         if (smem2 <= 128 * 1024 && !prepass_bulk_disabled()) {
-            static bool xattr = false;
-            if (!xattr) {
-                cudaFuncSetAttribute(x_to_digits_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     128 * 1024);
-                xattr = true;
-            }
+            NNE_TRY(ensure_dynamic_smem(ctx->device, x_to_digits_bulk_kernel, 128 * 1024));
             size_t per = (200 * 1024) / smem2;
             if (per > 6) per = 6;
             size_t nb = m;

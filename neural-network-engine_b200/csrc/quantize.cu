@@ -324,8 +324,7 @@ int launch_quantize_rows(nne_ctx *ctx, const float *w, size_t rows, size_t cols,
         if (per < 1) per = 1;
         size_t nblocks = rows;
         if (nblocks > (size_t)ctx->sm_count * per) nblocks = (size_t)ctx->sm_count * per;
-        NNE_CUDA_TRY(cudaFuncSetAttribute(quantize_rows_bulk_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+        NNE_TRY(ensure_dynamic_smem(ctx->device, quantize_rows_bulk_kernel, smem2));
         quantize_rows_bulk_kernel<<<(unsigned)nblocks, 256, smem2, s>>>(w, rows, cols, q, scales,
                                                                        ctx->err_word);
         NNE_LAUNCH_CHECK();
@@ -342,13 +341,11 @@ int launch_quantize_rows(nne_ctx *ctx, const float *w, size_t rows, size_t cols,
     size_t cap = (size_t)ctx->sm_count * per_sm;
     if (blocks > cap) blocks = cap;
     if (vec) {
-        NNE_CUDA_TRY(cudaFuncSetAttribute(quantize_rows_cta_kernel<true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NNE_TRY(ensure_dynamic_smem(ctx->device, quantize_rows_cta_kernel<true>, smem));
         quantize_rows_cta_kernel<true><<<(unsigned)blocks, 256, smem, s>>>(w, rows, cols, q, scales,
                                                                          cache_floats);
     } else {
-        NNE_CUDA_TRY(cudaFuncSetAttribute(quantize_rows_cta_kernel<false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        NNE_TRY(ensure_dynamic_smem(ctx->device, quantize_rows_cta_kernel<false>, smem));
         quantize_rows_cta_kernel<false><<<(unsigned)blocks, 256, smem, s>>>(w, rows, cols, q,
                                                                           scales, cache_floats);
     }

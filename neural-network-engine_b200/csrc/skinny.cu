@@ -388,7 +388,9 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {
                     if (r < m) {
-                        float v = sk_finish(s[r], __ldg(unscale + 2 * r), __ldg(unscale + 2 * r + 1), sc);
+                        // unscale[] is written by the pre-pass while this kernel may already be resident:
+                        // coherent loads, not the read-only path
+                        float v = sk_finish(s[r], __ldcg(unscale + 2 * r), __ldcg(unscale + 2 * r + 1), sc);
                         if (bias) v = __fadd_rn(v, bv);
                         y[(size_t)r * ldy + ch] = v;
                     }
@@ -524,7 +526,9 @@ bool skinny_supports(const nne_qlinear *ql, size_t m) {
 int skinny_prepare_layer(nne_qlinear *ql) {
     ql->tmap_wsk = nullptr;
     if (ql->n == 0 || ql->k == 0 || ql->k % 16 != 0) return NNE_OK;
-    if (ql->n > 0x7fffff00u || ql->k > 0x7fffff00u) return NNE_OK;
+    // One product is at most 128 * 64 = 2^13 in magnitude and a tile's int32 accumulator in TMEM
+    // adds k of them: exact only up to k = 2^18.  Longer rows go to the generic kernel.
+    if (ql->n > 0x7fffff00u || ql->k > NNE_TENSOR_INT_MAX_K) return NNE_OK;
     if ((reinterpret_cast<uintptr_t>(ql->q) & 15u) != 0) return NNE_OK;
     CUtensorMap *map = new CUtensorMap;
     int st = tma_make_map_2d(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, ql->q, ql->k, ql->n, SK_BKB, SK_BM,
@@ -544,14 +548,8 @@ void skinny_release_layer(nne_qlinear *ql) {
 
 namespace {
 
-int set_smem_attr() {
-    static bool attr_set = false;
-    if (!attr_set) {
-        NNE_CUDA_TRY(cudaFuncSetAttribute(qlinear_skinny_i8_kernel,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, SK_SMEM_BYTES));
-        attr_set = true;
-    }
-    return NNE_OK;
+int set_smem_attr(const nne_ctx *ctx) {
+    return ensure_dynamic_smem(ctx->device, qlinear_skinny_i8_kernel, SK_SMEM_BYTES);
 }
 
 size_t sk_tiles(size_t n) { return (n + SK_BM - 1) / SK_BM; }
@@ -576,7 +574,7 @@ void sk_fill_layer(SkLayer &L, const nne_qlinear *ql, float *y, size_t ldy) {
 int sk_launch(nne_ctx *ctx, const SkLayer *one, const SkLayer *many_dev, int count, const SkInput *in_one,
               const SkInput *in_many_dev, int in_count, size_t m, long long total, uint4 *zero_base,
               size_t zero_bytes, cudaStream_t s) {
-    NNE_TRY(set_smem_attr());
+    NNE_TRY(set_smem_attr(ctx));
     cudaLaunchAttribute pdl[1];
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     pdl[0].val.programmaticStreamSerializationAllowed = 1;

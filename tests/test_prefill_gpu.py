@@ -101,6 +101,61 @@ def test_config3_m2048_sampled_rows(nne, ctx):
     assert np.isfinite(y).all()
 
 
+@pytest.mark.parametrize("n,k,m", [(11008, 4096, 512), (4096, 11008, 512), (4096, 11008, 2048),
+                                   (11008, 4096, 8192), (4096, 11008, 8192)])
+def test_config3_remaining_sizes_sampled_rows(nne, ctx, n, k, m):
+    """The other sizes of config 3 (M = 512 and 8192 on both FFN shapes, 11008 -> 4096 at M = 2048):
+    activations drawn on the device, the forward through the device entry point, 48 sampled rows
+    (first and last included) against the oracle; every row is an independent contraction."""
+    import torch
+    ql, qo, so, b = layer(nne, ctx, 3, n, k, False)
+    assert ql.kernel_for(m) == 2
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3000 + m + n)
+    xd = torch.randn(m, k, generator=gen, device="cuda")
+    yd = torch.full((m, n), float("nan"), device="cuda")
+    ql.forward_device(xd.data_ptr(), m, yd.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    ctx.check()
+    rows = np.unique(np.concatenate([[0, m - 1], np.random.default_rng(m).choice(m, 46, replace=False)]))
+    idx = torch.from_numpy(rows).cuda()
+    x = xd[idx].cpu().numpy()
+    y = yd[idx].cpu().numpy()
+    y_ref = oracle.forward(qo, so, None, x)
+    xinf_all = float(xd.abs().max())
+    tol, _ = oracle.tolerance(qo, so, x)
+    err = np.abs(y - y_ref)
+    ratio = float((err / tol).max())
+    rms = float(np.sqrt((y_ref.astype(np.float64) ** 2).mean()))
+    print(f"config3 {k}->{n} M={m}: 48 sampled rows, max|err| {err.max():.3e}, max err/tol {ratio:.3e}, "
+          f"max|err|/rms(y) {err.max() / rms:.3e}, ||x||inf {xinf_all:.2f}")
+    assert ratio <= 1.0
+    assert bool(torch.isfinite(yd).all())
+
+
+def test_dominant_activation_on_the_prefill_grid(nne, ctx):
+    """One element of a row 500 times larger than the rest (LLM activations have such outliers): the
+    prefill kernel's fixed-point grid is per ROW, 2^-13 of the row's power-of-two ceiling, so the
+    small elements of that row lose most of their bits.  The result stays inside the tolerance by
+    construction (it scales with ||x||inf); the tight number, max|err| / rms(y), is printed."""
+    n, k, m = 1024, 4096, 64
+    ql, qo, so, b = layer(nne, ctx, 8, n, k, False)
+    x = oracle.normal(8, 1, (m, k))
+    x[5, 100] = 500.0
+    x[40, 7] = -3000.0
+    y = ql.forward(x)
+    ctx.check()
+    y_ref = oracle.forward(qo, so, None, x)
+    y64 = oracle.forward_f64(qo, so, None, x)
+    for r in (5, 40, 0):
+        tol_r, _ = oracle.tolerance(qo, so, x[r:r + 1])
+        err = np.abs(y[r] - y_ref[r])
+        rms = float(np.sqrt((y64[r] ** 2).mean()))
+        print(f"prefill row {r} (max|x| {np.abs(x[r]).max():.0f}): max|err| {err.max():.3e}, "
+              f"max err/tol {float((err / tol_r).max()):.3e}, max|err|/rms(y) {err.max() / rms:.3e}")
+        assert float((err / tol_r).max()) <= 1.0
+
+
 def test_strided_output_and_device_entry(nne, ctx):
     import torch
     n, k, m = 512, 256, 160

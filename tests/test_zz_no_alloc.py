@@ -55,6 +55,40 @@ def test_static_forward_matches_ordinary_forward_twice(nne, ctx):
         assert np.array_equal(y_new.cpu().numpy().view(np.uint32), y_ref.cpu().numpy().view(np.uint32))
 
 
+def test_static_forward_worst_case_stays_inside_its_own_bound(nne, ctx):
+    """The entry point's documented bound is the bf16 kernel's, 2^-8 * ||x||inf * scale_j * sum|q_jk|,
+    which is looser than the 1e-3 tolerance of the ordinary forward.  Activations that sit on bf16
+    half-way points (1 + 2^-8 rounds to 1), with signs chosen so that every rounding error pulls
+    channel 0 the same way, come close to that bound and stay inside it; the ordinary forward
+    (integer kernel) keeps its 1e-3 tolerance on the same input."""
+    import torch
+    lib = nne.load()
+    n, k, m = 256, 1024, 32
+    w = oracle.normal(123, 0, (n, k), 0.0, 0.02)
+    ql = nne.QLinear.from_linear(nne.Linear(w), ctx)
+    q = ql.qweight.reshape(n, k)
+    sign = np.where(q[0] >= 0, -1.0, 1.0).astype(np.float32)   # error of bf16(x_k) gets q's sign
+    x = np.tile((sign * np.float32(1.0 + 2.0 ** -8))[None, :], (m, 1)).astype(np.float32)
+    xd = torch.from_numpy(x).cuda()
+    y_new = torch.empty(m, n, device="cuda")
+    y_ord = torch.empty(m, n, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    assert lib.nne_qlinear_forward_dev_static(ql._handle, xd.data_ptr(), m, k, y_new.data_ptr(), s) == 0
+    assert lib.nne_qlinear_forward_dev(ql._handle, xd.data_ptr(), m, k, y_ord.data_ptr(), s) == 0
+    torch.cuda.synchronize()
+    ctx.check()
+    exact = oracle.forward_f64(q, ql.scales, None, x)
+    tol, xinf = oracle.tolerance(q, ql.scales, x)              # 1e-3 * ||x||inf * scale_j * sum|q_jk|
+    bound_bf16 = tol * (2.0 ** -8 / 1e-3)
+    err_new = np.abs(y_new.cpu().numpy() - exact)
+    err_ord = np.abs(y_ord.cpu().numpy() - exact)
+    print(f"bf16 worst case: channel 0 err / (1e-3 bound) = {float(err_new[0, 0] / tol[0]):.2f}, "
+          f"err / (2^-8 bound) = {float(err_new[0, 0] / bound_bf16[0]):.3f}")
+    assert float((err_new / (bound_bf16 * 1.001)).max()) <= 1.0
+    assert float(err_new[0, 0] / tol[0]) > 1.0    # the case really is outside the ordinary tolerance
+    assert float((err_ord / tol).max()) <= 1.0
+
+
 def test_static_forward_refuses_what_it_cannot_take(nne, ctx):
     import torch
     lib = nne.load()
