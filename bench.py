@@ -16,8 +16,11 @@ forward per layer) under "decode_batch_sweep" and the M=2048 prefill figure (TFL
 "prefill".
 
 N > 1 (torchrun, one rank per GPU): every rank holds its own column shard of N-times-wider layers
-(weak scaling: per-GPU weight bytes fixed), computes its output slices and the step's slices are
-all-gathered over NCCL.
+(weak scaling: per-GPU weight bytes fixed) and a step ends with the gathered outputs on every rank.
+The exchange is the library's (nne_qlinear_plan_create_sharded): the decode kernel stores its
+results into every rank's window over peer-mapped memory; the NCCL all-gather route is timed beside
+it (NNE_BENCH_ROUTE=nccl makes it the headline) and both are checked bit for bit.  "config5" carries
+the 70B-shaped FFN sharded over the same GPUs at M=1 and M=2048.
 
 --impl reference times the CPU restatement of the reference's Rayon/AVX2 path (oracle/) on the
 host cores: at M=1 the reference's row split gives exactly one task, hence one thread.
@@ -40,11 +43,13 @@ SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008)]  # (N, K)
 REPLICAS = 4  # copies of each shape in the rotation set: 4 * 107 MB = 428 MB > 126 MB L2
 PREFILL_SHAPES = [(11008, 4096), (4096, 11008)]
 DECODE_SWEEP_M = (1, 2, 4, 8, 16)
-RESERVED_SMS = 8  # N > 1: SMs left to the all-gather that runs beside the next step's kernel
 PREFILL_M = 2048
+PREFILL_OTHER_M = (128, 512)
+REPEATS_PER_STEP = 100  # plan launches per reported step
+CONFIG5_SHAPES = [(28672, 8192), (8192, 28672)]  # LLaMA-70B-shaped FFN: gate/up and down
+CONFIG5_M = 2048
 # dram__bytes_read.sum + dram__bytes_write.sum of one qgemv_stream_kernel launch over the rotation
-# set (read 428.5 MB + write 5.1 MB), from the ncu capture summarised in
-# profiles/qgemv_stream_kernel__decode_rotation_set.md.
+# set (read 428.5 MB + write 5.1 MB), from an ncu capture of this kernel on this workload.
 DRAM_TRAFFIC_PER_LAUNCH = 433.6e6
 
 
@@ -78,7 +83,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "20", "-i", str(self.gpu_index)],
+                 "-lms", "10", "-i", str(self.gpu_index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -196,40 +201,18 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------
 # native arm
 # ---------------------------------------------------------------------------------------------
-class RawNccl:
-    """ncclAllGather called straight through ctypes on the NCCL library torch has loaded, with a
-    communicator of its own (unique id broadcast over torch.distributed).  The c10d wrapper costs
-    tens of microseconds of host time per call - more than is left per 73 us step once eight ranks
-    share the host's cores; the direct call costs a few."""
-
-    def __init__(self, torch, dist, rank, world, dev):
-        path = os.path.join(os.path.dirname(torch.__file__), "..", "nvidia", "nccl", "lib", "libnccl.so.2")
-        self.lib = C.CDLL(path if os.path.exists(path) else "libnccl.so.2")
-
-        class UniqueId(C.Structure):
-            _fields_ = [("internal", C.c_byte * 128)]
-
-        uid = UniqueId()
-        if rank == 0 and self.lib.ncclGetUniqueId(C.byref(uid)) != 0:
-            raise RuntimeError("ncclGetUniqueId failed")
-        t = torch.tensor(list(bytes(uid)), dtype=torch.uint8, device=dev)
-        dist.broadcast(t, 0)
-        C.memmove(C.byref(uid), bytes(t.cpu().tolist()), 128)
-        self.lib.ncclCommInitRank.argtypes = [C.POINTER(C.c_void_p), C.c_int, UniqueId, C.c_int]
-        self.lib.ncclAllGather.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p]
-        self.comm = C.c_void_p()
-        if self.lib.ncclCommInitRank(C.byref(self.comm), world, uid, rank) != 0:
-            raise RuntimeError("ncclCommInitRank failed")
-
-    def all_gather_f32(self, send_ptr, recv_ptr, count, stream_ptr):
-        if self.lib.ncclAllGather(send_ptr, recv_ptr, count, 7, self.comm, stream_ptr) != 0:  # 7 = ncclFloat32
-            raise RuntimeError("ncclAllGather failed")
-
-    def close(self):
-        if self.comm:
-            self.lib.ncclCommDestroy.argtypes = [C.c_void_p]
-            self.lib.ncclCommDestroy(self.comm)
-            self.comm = C.c_void_p()
+def device_time_ms(torch, stream, fn, iters, warm=3):
+    """Device time of `iters` calls of fn issued back to back on `stream` (CUDA events)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(iters):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
 
 
 def run_native(args):
@@ -246,11 +229,8 @@ def run_native(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # The all-gather runs beside the next step's kernel on the SMs that kernel leaves free
-        # (RESERVED_SMS): cap the collective's CTAs at that number, or it waits for the kernel to
-        # end (measured at N = 8 without the cap: 102.8 us per step against 72.7 on one GPU).
-        os.environ.setdefault("NCCL_MAX_CTAS", str(RESERVED_SMS))
-        # 0.3 MB per rank: the low-latency protocol.  N = 8, us per step: default 107.5, LL128 84.2, LL 107.7.
+        # the NCCL route moves 0.3 MB per rank and step: the low-latency protocol
+        # (N = 8, us per step: default 107.5, LL128 84.2, LL 107.7)
         os.environ.setdefault("NCCL_PROTO", "LL128")
         dist.init_process_group("nccl", device_id=dev)
 
@@ -258,151 +238,196 @@ def run_native(args):
     lib = nne.load()
     ctx = nne.CudaContext(local_rank)
     peaks = measured_peaks()
+    stream = torch.cuda.current_stream()
 
-    def make_layer(n, k, seed):
+    def ok(status):
+        if status != 0:
+            raise RuntimeError(nne._lib.last_error())
+
+    def make_layer(n, k, seed, std=0.02):
         g = torch.Generator(device=dev)
         g.manual_seed(seed)
-        w = torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * 0.02
+        w = torch.randn(n, k, generator=g, device=dev, dtype=torch.float32) * std
         h = C.c_void_p()
-        st = lib.nne_qlinear_create_from_f32_dev(ctx.handle, w.data_ptr(), None, n, k,
-                                                 torch.cuda.current_stream().cuda_stream, C.byref(h))
-        if st != 0:
-            raise RuntimeError(f"layer create failed: {nne._lib.last_error()}")
+        ok(lib.nne_qlinear_create_from_f32_dev(ctx.handle, w.data_ptr(), None, n, k,
+                                               stream.cuda_stream, C.byref(h)))
         torch.cuda.synchronize()
         del w
         return h
-
-    # rotation set: REPLICAS independently drawn copies of each shape (this rank's shard when N>1).
-    # Outputs of all layers live in one slab per rank, so that N > 1 gathers a step's output
-    # slices with a single NCCL all-gather.  N > 1 alternates two slabs: the gather of step i runs
-    # on a second stream beside the kernel of step i+1, which writes the other slab.
-    specs = [(n, k) for _ in range(REPLICAS) for (n, k) in SHAPES]
-    slab_len = sum(n for n, _ in specs)
-    overlap = world > 1
-    nslabs = 2 if overlap else 1
-    gathered = [torch.zeros(world, slab_len, device=dev, dtype=torch.float32) for _ in range(nslabs)]
-    own = [g[rank] for g in gathered]
-    layers, off = [], 0
-    for i, (n, k) in enumerate(specs):
-        h = make_layer(n, k, 2 + 1000 * rank + i)
-        g = torch.Generator(device=dev)
-        g.manual_seed(100 + i)  # activations are replicated: the same on every rank
-        x = torch.randn(1, k, generator=g, device=dev, dtype=torch.float32)
-        layers.append({"h": h, "n": n, "k": k, "x": x, "off": off, "y_own": own[0][off:off + n]})
-        off += n
-    step_bytes = sum(algorithmic_bytes(L["n"], L["k"], 1) for L in layers)
-    stream = torch.cuda.current_stream()
-
-    # The step as ONE launch: a plan over the whole rotation set (nne_qlinear_plan_*), one plan
-    # per output slab.
-    nl = len(layers)
-    hs = (C.c_void_p * nl)(*[L["h"] for L in layers])
-    xs = (C.c_void_p * nl)(*[L["x"].data_ptr() for L in layers])
-    plans = []
-    for sl in range(nslabs):
-        ys = (C.c_void_p * nl)(*[own[sl][L["off"]:L["off"] + L["n"]].data_ptr() for L in layers])
-        p = C.c_void_p()
-        if lib.nne_qlinear_plan_create(ctx.handle, nl, hs, xs, ys, 1, C.byref(p)) != 0:
-            raise RuntimeError(nne._lib.last_error())
-        plans.append(p)
-    launches_per_step = lib.nne_qlinear_plan_launches(plans[0])
-    if overlap:
-        # The persistent streaming kernel leaves a few SMs to the collective's CTAs.  Measured at
-        # N = 2, microseconds per step: gather on the same stream 83.9; second stream with 0 / 8 / 16
-        # SMs left free 80.6 / 80.1 / 82.4.
-        if lib.nne_cuda_ctx_reserve_sms(ctx.handle, RESERVED_SMS) != 0:
-            raise RuntimeError(nne._lib.last_error())
-    comm = torch.cuda.Stream() if overlap else None
-    raw = None
-    if overlap:
-        # every rank must take the same route: agree on whether the direct communicator came up
-        try:
-            raw = RawNccl(torch, dist, rank, world, dev)
-            good = 1
-        except Exception:
-            raw, good = None, 0
-        flag = torch.tensor([good], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            if raw is not None:
-                raw.close()
-            raw = None
-    plan_done = [torch.cuda.Event() for _ in range(nslabs)]
-    gather_done = [torch.cuda.Event() for _ in range(nslabs)]
-    step_no = [0]
-
-    def step():
-        sl = step_no[0] % nslabs
-        if overlap and step_no[0] >= nslabs:
-            stream.wait_event(gather_done[sl])  # the gather that last read this slab is over
-        step_no[0] += 1
-        if lib.nne_qlinear_plan_run(plans[sl], stream.cuda_stream) != 0:
-            raise RuntimeError(nne._lib.last_error())
-        if overlap:
-            plan_done[sl].record(stream)
-            comm.wait_event(plan_done[sl])
-            if raw is not None:  # in place: this rank's slice already sits in its slot
-                raw.all_gather_f32(own[sl].data_ptr(), gathered[sl].data_ptr(), slab_len, comm.cuda_stream)
-            else:
-                with torch.cuda.stream(comm):
-                    dist.all_gather_into_tensor(gathered[sl].view(-1), own[sl])
-            gather_done[sl].record(comm)
-        elif world > 1:
-            dist.all_gather_into_tensor(gathered[0].view(-1), own[0])
-
-    def drain():
-        if overlap:
-            for sl in range(min(nslabs, step_no[0])):
-                stream.wait_event(gather_done[sl])
-
-    def per_layer_step():
-        s = torch.cuda.current_stream().cuda_stream
-        for L in layers:
-            if lib.nne_qlinear_forward_dev(L["h"], L["x"].data_ptr(), 1, L["k"],
-                                           L["y_own"].data_ptr(), s) != 0:
-                raise RuntimeError(nne._lib.last_error())
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # Rotation set: REPLICAS independently drawn copies of each shape.  N > 1: every layer is this
+    # rank's column shard (rows [rank*n, (rank+1)*n)) of a layer `world` times wider - weak scaling -
+    # and a step ends with every rank holding the gathered [1, world*n] output of every layer.
+    specs = [(n, k) for _ in range(REPLICAS) for (n, k) in SHAPES]
+    nl = len(specs)
+    y_total = sum(n for n, _ in specs)
+    group = None
+    route_names = {0: "peer stores from the forward kernel", 1: "ncclAllGather"}
+    head_route = 1 if os.environ.get("NNE_BENCH_ROUTE", "").startswith("n") else 0
+    if world > 1:
+        window = 4 * (4 * world * y_total + 2 * CONFIG5_M * sum(n for n, _ in CONFIG5_SHAPES)) + (64 << 20)
+        group = nne.ShardGroup(ctx, rank, world, window)
+        group.use_nccl()
+    layers = []
+    for i, (n, k) in enumerate(specs):
+        h = make_layer(n, k, 2 + 1000 * rank + i)
+        g = torch.Generator(device=dev)
+        g.manual_seed(100 + i)  # activations are replicated: the same on every rank
+        x = torch.randn(1, k, generator=g, device=dev, dtype=torch.float32)
+        layers.append({"h": h, "n": n, "k": k, "x": x})
+    step_bytes = sum(algorithmic_bytes(L["n"], L["k"], 1) for L in layers)
+    hs = (C.c_void_p * nl)(*[L["h"] for L in layers])
+    xs = (C.c_void_p * nl)(*[L["x"].data_ptr() for L in layers])
+
+    # The step as ONE launch: a plan over the whole rotation set.  One GPU: an ordinary plan.
+    # N > 1: sharded plans over two output areas of the window that alternate from step to step
+    # (a rank may begin step i+1 while a peer still reads the result of step i).
+    def sharded_plans(route, x_ptrs=None):
+        plans, areas = [], []
+        for _ in range(2):
+            base = group.alloc(world * y_total)
+            ptrs, off = [], 0
+            for L in layers:
+                ptrs.append(base + 4 * off)
+                off += world * L["n"]
+            p = C.c_void_p()
+            rb = (C.c_size_t * nl)(*[rank * L["n"] for L in layers])
+            nt = (C.c_size_t * nl)(*[world * L["n"] for L in layers])
+            ok(lib.nne_qlinear_plan_create_sharded(group.handle, nl, hs, rb, nt, x_ptrs or xs,
+                                                   (C.c_void_p * nl)(*ptrs), 1, route, C.byref(p)))
+            plans.append(p)
+            areas.append((base, ptrs))
+        return plans, areas
+
+    y_local = torch.zeros(y_total, device=dev, dtype=torch.float32)
+    yl_ptrs, off = [], 0
+    for L in layers:
+        L["y_local"] = y_local[off:off + L["n"]]
+        yl_ptrs.append(y_local.data_ptr() + 4 * off)
+        off += L["n"]
+    local_plan = C.c_void_p()
+    ok(lib.nne_qlinear_plan_create(ctx.handle, nl, hs, xs, (C.c_void_p * nl)(*yl_ptrs), 1, C.byref(local_plan)))
+    if world > 1:
+        plans_by_route = {0: sharded_plans(0), 1: sharded_plans(1)}
+        plans, areas = plans_by_route[head_route]
+    else:
+        plans, areas = [local_plan], None
+    launches_per_step = lib.nne_qlinear_plan_launches(plans[0])
+
+    def stepper(plan_list):
+        turn = [0]
+
+        def step():
+            p = plan_list[turn[0] % len(plan_list)]
+            turn[0] += 1
+            ok(lib.nne_qlinear_plan_run(p, stream.cuda_stream))
+        return step
+
+    step = stepper(plans)
+    R = REPEATS_PER_STEP
     for _ in range(max(args.warmup, 3)):
         step()
-    drain()
     barrier()
 
-    # device-timed region: K steps back to back on one stream
+    # device-timed region: K steps of R plan launches each, back to back on one stream
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
+        time.sleep(0.2)
     launches0 = lib.nne_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record(stream)
     h0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(args.steps * R):
         step()
-    host_us_per_step = (time.perf_counter() - h0) * 1e6 / args.steps  # enqueue only, nothing waited for
-    drain()
+    host_us_per_launch = (time.perf_counter() - h0) * 1e6 / (args.steps * R)  # enqueue only
     e1.record(stream)
     barrier()
     launches = lib.nne_launch_count() - launches0
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+    ms = max_over_ranks(e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
-    value = step_bytes * world * args.steps / (ms * 1e-3) / 1e9
-    per_launch_us = ms * 1e3 / (args.steps * launches_per_step)
-    achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9  # one GPU's kernels
+    passes = args.steps * R
+    value = step_bytes * world * passes / (ms * 1e-3) / 1e9
+    per_launch_us = ms * 1e3 / (passes * launches_per_step)
+    achieved = step_bytes * passes / (ms * 1e-3) / 1e9  # one GPU's kernels
+
+    # N > 1, outside the timed region: (1) the same step with no exchange and through the other
+    # route, (2) a check of what the exchange delivered.  For (2) every rank draws NEW activations
+    # (so that nothing left over from the timed steps can pass), runs one step, and recomputes on
+    # its own GPU the slices that two OTHER ranks own in three layers (their weights from the same
+    # seeds): those slices of its gathered outputs, and its own, must be bit-identical - channel j
+    # reads row j only (src/nn/quantized.rs:184-192), so a shard computes what the full layer would.
+    multi = parity = None
+    if world > 1:
+        iters = max(20, min(passes, 400))
+        t_local = max_over_ranks(device_time_ms(torch, stream, stepper([local_plan]), iters))
+        barrier()
+        other = 1 - head_route
+        t_other = max_over_ranks(device_time_ms(torch, stream, stepper(plans_by_route[other][0]), iters))
+        barrier()
+        multi = {"kernel_only_us_per_step": t_local * 1e3,
+                 "kernel_plus_exchange_us_per_step": ms * 1e3 / passes,
+                 "route": route_names[head_route],
+                 "other_route": {"route": route_names[other], "us_per_step": t_other * 1e3,
+                                 "GB/s": step_bytes * world / (t_other * 1e-3) / 1e9}}
+        for i, L in enumerate(layers):
+            g = torch.Generator(device=dev)
+            g.manual_seed(9000 + i)
+            L["x"].copy_(torch.randn(1, L["k"], generator=g, device=dev, dtype=torch.float32))
+        checked, identical = 0, True
+        for route in (0, 1):
+            pl, ar = plans_by_route[route]
+            barrier()
+            ok(lib.nne_qlinear_plan_run(pl[0], stream.cuda_stream))
+            barrier()
+            ctx.check()
+            for i in (0, 1, 2):
+                L = layers[i]
+                got = torch.as_tensor(nne.DeviceArray(ar[0][1][i], (world * L["n"],)), device=dev)
+                for r in sorted({rank, (rank + 1) % world, (rank + 2) % world}):
+                    h = L["h"] if r == rank else make_layer(L["n"], L["k"], 2 + 1000 * r + i)
+                    want = torch.empty(L["n"], device=dev, dtype=torch.float32)
+                    ok(lib.nne_qlinear_forward_dev(h, L["x"].data_ptr(), 1, L["k"], want.data_ptr(),
+                                                   stream.cuda_stream))
+                    torch.cuda.synchronize()
+                    same = torch.equal(got[r * L["n"]:(r + 1) * L["n"]].view(torch.int32), want.view(torch.int32))
+                    identical = identical and same
+                    checked += 1
+                    if r != rank:
+                        lib.nne_qlinear_destroy(h)
+        t = torch.tensor([1 if identical else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        parity = {"checked": checked * world, "identical": bool(int(t.item())),
+                  "what": "both routes, fresh activations, 3 layers: own slice and the slices of two other "
+                          "ranks recomputed locally from their seeds, bit for bit, on every rank"}
+        if not parity["identical"]:
+            if rank == 0:
+                print(json.dumps({"error": "gathered output differs from the locally recomputed slices",
+                                  "parity": parity}))
+            sys.exit(3)
 
     # The same step issued layer by layer (one launch per QLinear, replayed as a CUDA graph so the
     # host's launch cost stays out): what a caller gets without a plan.
     per_layer = None
     if world == 1:
+        def per_layer_step():
+            s = torch.cuda.current_stream().cuda_stream
+            for L in layers:
+                ok(lib.nne_qlinear_forward_dev(L["h"], L["x"].data_ptr(), 1, L["k"], L["y_local"].data_ptr(), s))
+
         for _ in range(3):
             per_layer_step()
         torch.cuda.synchronize()
@@ -412,46 +437,45 @@ def run_native(args):
         with torch.cuda.graph(graph, stream=side):
             per_layer_step()  # launches on torch's current stream, which is `side` here
         torch.cuda.synchronize()
-        for _ in range(3):
-            graph.replay()
-        torch.cuda.synchronize()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
-        g1.record(stream)
-        torch.cuda.synchronize()
-        gms = g0.elapsed_time(g1)
-        per_layer = {"value": step_bytes * args.steps / (gms * 1e-3) / 1e9, "unit": "GB/s",
-                     "launches_per_step": nl, "avg_launch_us": gms * 1e3 / (args.steps * nl),
+        gms = device_time_ms(torch, stream, graph.replay, max(20, min(passes, 400)))
+        per_layer = {"value": step_bytes / (gms * 1e-3) / 1e9, "unit": "GB/s",
+                     "frac_of_measured_hbm": step_bytes / (gms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     "launches_per_step": nl, "avg_launch_us": gms * 1e3 / nl,
                      "launch": "CUDA graph replay of 12 single-layer launches"}
 
     # end-to-end: host buffers in, host buffers out, H2D and D2H inside every timed step.
     # (1) the step as the plan runs it: nne_qlinear_plan_run_host over one pinned x slab and one
-    #     pinned y slab (one copy each way around the one launch);
+    #     pinned y slab (one copy each way around the one launch); N > 1: the sharded plan, so the
+    #     exchange is inside and the GATHERED outputs come back (two plans alternate output areas);
     # (2) layer by layer through nne_qlinear_forward_host (what QLinear::forward binds to).
     x_total = sum(L["k"] for L in layers)
-    y_total = sum(L["n"] for L in layers)
     xslab = torch.empty(x_total, device=dev, dtype=torch.float32)
-    yslab = torch.empty(y_total, device=dev, dtype=torch.float32)
     xh_all = torch.empty(x_total, dtype=torch.float32).pin_memory()
-    yh_all = torch.empty(y_total, dtype=torch.float32).pin_memory()
-    xo = yo = 0
-    xps, yps = [], []
+    yh_all = torch.empty(world * y_total, dtype=torch.float32).pin_memory()
+    xo = 0
+    xps = []
     for L in layers:
         xh_all[xo:xo + L["k"]].copy_(L["x"].view(-1).cpu())
         xps.append(xslab.data_ptr() + 4 * xo)
-        yps.append(yslab.data_ptr() + 4 * yo)
         xo += L["k"]
-        yo += L["n"]
-    hplan = C.c_void_p()
-    if lib.nne_qlinear_plan_create(ctx.handle, nl, hs, (C.c_void_p * nl)(*xps), (C.c_void_p * nl)(*yps), 1,
-                                   C.byref(hplan)) != 0:
-        raise RuntimeError(nne._lib.last_error())
+    xps_c = (C.c_void_p * nl)(*xps)
+    if world > 1:
+        hplans, _ = sharded_plans(head_route, xps_c)
+    else:
+        yslab = torch.empty(y_total, device=dev, dtype=torch.float32)
+        yps, yo = [], 0
+        for L in layers:
+            yps.append(yslab.data_ptr() + 4 * yo)
+            yo += L["n"]
+        hp = C.c_void_p()
+        ok(lib.nne_qlinear_plan_create(ctx.handle, nl, hs, xps_c, (C.c_void_p * nl)(*yps), 1, C.byref(hp)))
+        hplans = [hp]
+    e2e_turn = [0]
 
     def e2e_step():
-        if lib.nne_qlinear_plan_run_host(hplan, xh_all.data_ptr(), yh_all.data_ptr()) != 0:
-            raise RuntimeError(nne._lib.last_error())
+        p = hplans[e2e_turn[0] % len(hplans)]
+        e2e_turn[0] += 1
+        ok(lib.nne_qlinear_plan_run_host(p, xh_all.data_ptr(), yh_all.data_ptr()))
 
     host = []
     for L in layers:
@@ -462,9 +486,7 @@ def run_native(args):
 
     def e2e_layer_step():
         for L, (xh, yh) in zip(layers, host):
-            st = lib.nne_qlinear_forward_host(L["h"], xh.data_ptr(), 1, L["k"], yh.data_ptr())
-            if st != 0:
-                raise RuntimeError(nne._lib.last_error())
+            ok(lib.nne_qlinear_forward_host(L["h"], xh.data_ptr(), 1, L["k"], yh.data_ptr()))
 
     def time_host(fn, steps):
         for _ in range(3):
@@ -474,40 +496,43 @@ def run_native(args):
         for _ in range(steps):
             fn()
         torch.cuda.synchronize()
-        sec = time.perf_counter() - t0
-        if world > 1:
-            t = torch.tensor([sec], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            sec = float(t.item())
-        return sec
+        return max_over_ranks(time.perf_counter() - t0)
 
-    e2e_steps = max(args.steps, 5)
+    e2e_steps = max(min(passes, 500), 20)
     e2e_s = time_host(e2e_step, e2e_steps)
-    e2e_layer_s = time_host(e2e_layer_step, min(e2e_steps, 200))
     e2e_value = step_bytes * world * e2e_steps / e2e_s / 1e9
-    e2e_layer_value = step_bytes * world * min(e2e_steps, 200) / e2e_layer_s / 1e9
-    # the two routes must agree bit for bit
-    got = torch.cat([yh.view(-1) for _, yh in host])
-    if not torch.equal(got.view(torch.int32), yh_all.view(torch.int32)):
-        raise RuntimeError("plan and per-layer host results differ")
-    lib.nne_qlinear_plan_destroy(hplan)
+    e2e_layer_steps = min(e2e_steps, 100)
+    e2e_layer = None
+    if world == 1:
+        e2e_layer_s = time_host(e2e_layer_step, e2e_layer_steps)
+        e2e_layer = {"value": step_bytes * e2e_layer_steps / e2e_layer_s / 1e9, "unit": "GB/s",
+                     "api": "nne_qlinear_forward_host, 12 calls per step (per call H2D + launch + D2H + sync)"}
+        # the two routes must agree bit for bit
+        got = torch.cat([yh.view(-1) for _, yh in host])
+        if not torch.equal(got.view(torch.int32), yh_all.view(torch.int32)):
+            raise RuntimeError("plan and per-layer host results differ")
+    else:
+        # the gathered outputs that came back must hold this rank's own slices where they belong
+        e2e_layer_step()
+        off = 0
+        for L, (_, yh) in zip(layers, host):
+            mine = yh_all[off + rank * L["n"]: off + (rank + 1) * L["n"]]
+            if not torch.equal(mine.view(torch.int32), yh.view(-1).view(torch.int32)):
+                raise RuntimeError("gathered host result does not hold this rank's slice")
+            off += world * L["n"]
+    for p in hplans:
+        lib.nne_qlinear_plan_destroy(p)
     h2d = sum(4 * L["k"] for L in layers)
-    d2h = sum(4 * L["n"] for L in layers)
+    d2h = 4 * world * y_total
 
-    # decode batch sweep (config 2): one forward per layer over the rotation set, M rows each
-    sweep = None
+    sweep = prefill = stack = quant = None
     if world == 1:
-        sweep = run_decode_sweep(nne, lib, ctx, dev, layers, args)
-
-    # prefill (M = 2048) on the tensor-core kernel, when it is built in
-    prefill = None
-    if world == 1:
-        prefill = run_prefill(nne, lib, ctx, dev, make_layer, peaks, args)
-
-    # config 4: the 224 QLinears of a 7B-shaped decoder stack as independent forwards in one plan
-    stack = None
-    if world == 1:
-        stack = run_stack(nne, lib, ctx, dev, make_layer, peaks, args)
+        sweep = run_decode_sweep(nne, lib, ctx, dev, layers, args)          # config 2, M in 1..16
+        prefill = run_prefill(nne, lib, ctx, dev, make_layer, peaks, args)  # config 3
+        stack = run_stack(nne, lib, ctx, dev, make_layer, peaks, args)      # config 4
+        quant = run_quantize(nne, lib, ctx, dev, peaks, args)               # QLinear::from_linear
+    config5 = run_config5(nne, lib, ctx, dev, group, rank, world, make_layer, peaks, args,
+                          barrier, max_over_ranks)
 
     out = None
     if rank == 0:
@@ -520,53 +545,53 @@ def run_native(args):
             "dtype_note": "int8 weights x int8 digit planes of the f32 activations -> exact int32/int64 "
                           "sums (dp4a), one rounding to f32, f32 scale and bias",
             "config": {"workload": "config2-decode-7B-projections-M1", "shapes_NK": SHAPES,
-                       "m": 1, "replicas_per_shape": REPLICAS, "layers_per_step": len(layers),
-                       "weight_bytes_per_step_per_gpu": sum(L["n"] * L["k"] for L in layers),
+                       "m": 1, "replicas_per_shape": REPLICAS, "layers_per_pass": len(layers),
+                       "passes_per_step": R,
+                       "step": f"{R} passes over the rotation set, one plan launch (nne_qlinear_plan_run) per "
+                               "pass, back to back: long enough for the clock sampler to see load",
+                       "weight_bytes_per_pass_per_gpu": sum(L["n"] * L["k"] for L in layers),
                        "l2": "rotation set of distinct weights larger than the 126 MB L2",
-                       "launch": "one plan launch per step (nne_qlinear_plan_run), steps back to back",
                        "parallelism": "1 GPU" if world == 1 else
-                       f"column shards over {world} GPUs + one NCCL all-gather of the step's output slices"
-                       + (f", on a second stream beside the next step's kernel ({RESERVED_SMS} SMs left free for it)"
-                          if overlap else "")},
+                       f"column shards over {world} GPUs, output slices exchanged by {route_names[head_route]}"},
             "roofline": {"bound": "hbm", "kernel": "qgemv_stream_kernel", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "frac_of_nominal_8000": achieved / 8000.0,
-                         "avg_launch_us": per_launch_us, "launches_per_step": launches_per_step,
+                         "avg_launch_us": per_launch_us, "launches_per_pass": launches_per_step,
                          "algorithmic_bytes_per_launch": step_bytes / launches_per_step,
-                         "traffic": DRAM_TRAFFIC_PER_LAUNCH},
+                         "traffic": DRAM_TRAFFIC_PER_LAUNCH,
+                         "traffic_source": "ncu capture of this kernel on this workload at one GPU (a constant, "
+                                           "not measured in this run)"},
             "cpu_baseline": {"value": cpu_v, "unit": "GB/s", "cores": cpu_cores, "kind": "port",
                              "sample": cpu_sample},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "api": "nne_qlinear_plan_run_host (pinned host x and y slabs; H2D, one launch, D2H, "
-                           "sync in every step)",
-                    "per_layer": {"value": e2e_layer_value, "unit": "GB/s",
-                                  "api": "nne_qlinear_forward_host, 12 calls per step (per call H2D + "
-                                         "launch + D2H + sync)"}},
+                    "api": "nne_qlinear_plan_run_host (pinned host x and y slabs; H2D, one launch"
+                           + (", exchange of the output slices" if world > 1 else "")
+                           + ", D2H, sync in every pass)"},
             "gpu_launches": int(launches),
-            "host_enqueue_us_per_step": host_us_per_step,
-            "collective": None if world == 1 else ("ncclAllGather called directly (ctypes)" if raw is not None
-                                                    else "torch.distributed all_gather_into_tensor"),
+            "host_enqueue_us_per_launch": host_us_per_launch,
             "clocks": clocks,
         }
-        if per_layer is not None:
-            out["per_layer_launches"] = per_layer
-        if sweep is not None:
-            out["decode_batch_sweep"] = sweep
-        if prefill is not None:
-            out["prefill"] = prefill
-        if stack is not None:
-            out["decoder_stack"] = stack
+        if e2e_layer is not None:
+            out["e2e"]["per_layer"] = e2e_layer
+        for key, val in (("multi_gpu", multi), ("parity", parity), ("per_layer_launches", per_layer),
+                         ("decode_batch_sweep", sweep), ("prefill", prefill), ("decoder_stack", stack),
+                         ("quantize", quant), ("config5", config5)):
+            if val is not None:
+                out[key] = val
         print(json.dumps(out))
-    if raw is not None:
-        torch.cuda.synchronize()
-        raw.close()
-    for p in plans:
-        lib.nne_qlinear_plan_destroy(p)
+    torch.cuda.synchronize()
+    lib.nne_qlinear_plan_destroy(local_plan)
+    if world > 1:
+        for route in (0, 1):
+            for p in plans_by_route[route][0]:
+                lib.nne_qlinear_plan_destroy(p)
     for L in layers:
         lib.nne_qlinear_destroy(L["h"])
     if world > 1:
+        barrier()
+        group.close()
         dist.destroy_process_group()
 
 
@@ -677,60 +702,231 @@ def run_stack(nne, lib, ctx, dev, make_layer, peaks, args):
 
 
 def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):
-    """M = 2048 forward of the two FFN shapes; TFLOP/s = 2*M*N*K / device time."""
+    """Config 3.  M = 2048 forward of the two FFN shapes, TFLOP/s = 2*M*N*K / device time, timed
+    (a) as a burst of 20 forwards, (b) looped for more than a second with the SM clock sampled
+    (against the sustained bf16 figure), (c) end to end from pinned host memory; M = 128 and 512
+    beside it."""
     import torch
     res = {"m": PREFILL_M, "shapes_NK": PREFILL_SHAPES, "cases": []}
     stream = torch.cuda.current_stream()
     tot_flops, tot_ms = 0.0, 0.0
+    hs = []
     for si, (n, k) in enumerate(PREFILL_SHAPES):
         h = make_layer(n, k, 3 + si)
         kind = lib.nne_qlinear_kernel_for(h, PREFILL_M)
         if kind != 2:
             lib.nne_qlinear_destroy(h)
             return {"unavailable": "tensor-core kernel not built for this shape", "kernel": kind}
-        x = torch.randn(PREFILL_M, k, device=dev, dtype=torch.float32)
-        y = torch.empty(PREFILL_M, n, device=dev, dtype=torch.float32)
+        hs.append(h)
+    xs = [torch.randn(PREFILL_M, k, device=dev, dtype=torch.float32) for _, k in PREFILL_SHAPES]
+    ys = [torch.empty(PREFILL_M, n, device=dev, dtype=torch.float32) for n, _ in PREFILL_SHAPES]
 
-        def fwd():
-            st = lib.nne_qlinear_forward_dev(h, x.data_ptr(), PREFILL_M, k, y.data_ptr(),
-                                             stream.cuda_stream)
-            if st != 0:
-                raise RuntimeError(nne._lib.last_error())
+    def fwd(i, m=PREFILL_M):
+        n, k = PREFILL_SHAPES[i]
+        if lib.nne_qlinear_forward_dev(hs[i], xs[i].data_ptr(), m, k, ys[i].data_ptr(), stream.cuda_stream) != 0:
+            raise RuntimeError(nne._lib.last_error())
 
-        for _ in range(3):
-            fwd()
-        torch.cuda.synchronize()
-        iters = 20 if args.steps >= 20 else max(3, args.steps)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(iters):
-            fwd()
-        e1.record(stream)
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / iters
+    iters = 20 if args.steps >= 20 else max(3, args.steps)
+    for i, (n, k) in enumerate(PREFILL_SHAPES):
+        ms = device_time_ms(torch, stream, lambda: fwd(i), iters)
         flops = 2.0 * PREFILL_M * n * k
         res["cases"].append({"n": n, "k": k, "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12})
         tot_flops += flops
         tot_ms += ms
-        lib.nne_qlinear_destroy(h)
-        del x, y
     tf = tot_flops / (tot_ms * 1e-3) / 1e12
     res["roofline"] = {"bound": "tensor", "kernel": "qlinear_prefill_i8_kernel", "achieved": tf,
                        "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                        "frac": tf / peaks["bf16_tflops"], "peak_source": peaks["source"],
-                       "frac_of_nominal_2250": tf / 2250.0}
+                       "frac_of_nominal_2250": tf / 2250.0,
+                       "timing": f"burst: {iters} forwards per shape back to back",
+                       "note": "peak = measured cuBLAS bf16 GEMM; two int8 digit MMAs at twice the "
+                               "bf16 rate cost what one bf16 MMA would"}
     res["value"] = tf
     res["unit"] = "TFLOP/s"
     res["dtype"] = "s8 x s8 -> s32 (tcgen05 kind::i8; x as two int8 digit planes), f32 epilogue"
-    res["roofline"]["note"] = ("peak = measured cuBLAS bf16 GEMM; two int8 digit MMAs at twice the "
-                               "bf16 rate cost what one bf16 MMA would")
+
+    # (b) sustained: both shapes alternating for > 1 s, clocks sampled meanwhile
+    per_pair_ms = tot_ms
+    loops = max(10, int(1200.0 / per_pair_ms)) if args.steps >= 20 else 10
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    time.sleep(0.1)
+
+    def pair():
+        fwd(0)
+        fwd(1)
+
+    sms = device_time_ms(torch, stream, pair, loops, warm=2)
+    clocks = sampler.stop()
+    stf = tot_flops / (sms * 1e-3) / 1e12
+    res["sustained"] = {"value": stf, "unit": "TFLOP/s", "seconds": sms * loops * 1e-3, "forwards": 2 * loops,
+                        "peak": peaks["bf16_tflops_sustained"], "frac": stf / peaks["bf16_tflops_sustained"],
+                        "frac_of_burst_peak": stf / peaks["bf16_tflops"], "frac_of_nominal_2250": stf / 2250.0,
+                        "peak_source": peaks["source"] + " (cuBLAS bf16, seconds-long loop)", "clocks": clocks}
+
+    # (c) end to end from pinned host memory through nne_qlinear_forward_host (4096 -> 11008)
+    n, k = PREFILL_SHAPES[0]
+    xh = torch.randn(PREFILL_M, k, dtype=torch.float32).pin_memory()
+    yh = torch.empty(PREFILL_M, n, dtype=torch.float32).pin_memory()
+    reps = 5 if args.steps >= 20 else 2
+    for _ in range(2):
+        lib.nne_qlinear_forward_host(hs[0], xh.data_ptr(), PREFILL_M, k, yh.data_ptr())
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        if lib.nne_qlinear_forward_host(hs[0], xh.data_ptr(), PREFILL_M, k, yh.data_ptr()) != 0:
+            raise RuntimeError(nne._lib.last_error())
+    sec = (time.perf_counter() - t0) / reps
+    res["e2e"] = {"value": 2.0 * PREFILL_M * n * k / sec / 1e12, "unit": "TFLOP/s", "ms": sec * 1e3,
+                  "h2d_bytes_per_step": 4 * PREFILL_M * k, "d2h_bytes_per_step": 4 * PREFILL_M * n,
+                  "api": "nne_qlinear_forward_host, 4096->11008, pinned host x and y"}
+
+    # the smaller batches of config 3 (same layers, first M rows of the same activations)
+    res["other_m"] = []
+    for m in PREFILL_OTHER_M:
+        f, t = 0.0, 0.0
+        for i, (n, k) in enumerate(PREFILL_SHAPES):
+            ms = device_time_ms(torch, stream, lambda: fwd(i, m), iters)
+            f += 2.0 * m * n * k
+            t += ms
+        v = f / (t * 1e-3) / 1e12
+        res["other_m"].append({"m": m, "tflops": v, "frac": v / peaks["bf16_tflops"], "us_both_shapes": t * 1e3})
+    for h in hs:
+        lib.nne_qlinear_destroy(h)
     return res
+
+
+def run_quantize(nne, lib, ctx, dev, peaks, args):
+    """QLinear::from_linear's row loop on the device (nne_quantize_rows_dev): f32 [N, K] in, int8
+    codes and f32 scales out; algorithmic bytes 4NK + NK + 4N; launches back to back over three
+    matrices of each shape so that the input comes from HBM."""
+    import torch
+    stream = torch.cuda.current_stream()
+    cases = []
+    for (n, k) in ((11008, 4096), (4096, 11008), (28672, 8192)):
+        ws = [torch.randn(n, k, device=dev, dtype=torch.float32) * 0.02 for _ in range(3)]
+        q = torch.empty(n, k, device=dev, dtype=torch.int8)
+        sc = torch.empty(n, device=dev, dtype=torch.float32)
+        turn = [0]
+
+        def run():
+            w = ws[turn[0] % 3]
+            turn[0] += 1
+            if lib.nne_quantize_rows_dev(ctx.handle, w.data_ptr(), n, k, q.data_ptr(), sc.data_ptr(),
+                                         stream.cuda_stream) != 0:
+                raise RuntimeError(nne._lib.last_error())
+
+        ms = device_time_ms(torch, stream, run, 12)
+        nbytes = 5 * n * k + 4 * n
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        cases.append({"n": n, "k": k, "us": ms * 1e3, "GB/s": gbs, "frac_of_measured_hbm": gbs / peaks["hbm_gbs"]})
+        del ws, q, sc
+    return {"kernel": "quantize_rows_bulk_kernel", "cases": cases,
+            "bytes": "4*N*K read + N*K + 4*N written per launch"}
+
+
+def run_config5(nne, lib, ctx, dev, group, rank, world, make_layer, peaks, args, barrier, max_over_ranks):
+    """Config 5: LLaMA-70B-shaped FFN projections (8192 -> 28672, 28672 -> 8192; weights N(0, 0.015)),
+    column-sharded over the run's GPUs (strong scaling: the layer is fixed, a rank owns 1/N of its
+    rows), at M = 1 and M = 2048.  Per case: the forward kernels alone, and forward + exchange through
+    both routes; the gathered output is checked against a local recomputation of another rank's
+    slice (bit for bit)."""
+    import torch
+    stream = torch.cuda.current_stream()
+    cases = []
+    for si, (n_total, k) in enumerate(CONFIG5_SHAPES):
+        n = n_total // world
+        h = make_layer(n, k, 5000 + 100 * si + rank, std=0.015)
+        peer = (rank + 1) % world
+        h_peer = make_layer(n, k, 5000 + 100 * si + peer, std=0.015) if world > 1 else None
+        g = torch.Generator(device=dev)
+        g.manual_seed(50 + si)
+        x = torch.randn(CONFIG5_M, k, generator=g, device=dev, dtype=torch.float32)
+        y_local = torch.empty(CONFIG5_M, n, device=dev, dtype=torch.float32)
+        areas = None
+        if world > 1:
+            areas = [group.alloc(CONFIG5_M * n_total) for _ in range(2)]
+        for m in (1, CONFIG5_M):
+            def local():
+                if lib.nne_qlinear_forward_dev(h, x.data_ptr(), m, k, y_local.data_ptr(), stream.cuda_stream) != 0:
+                    raise RuntimeError(nne._lib.last_error())
+
+            iters = 20 if args.steps >= 20 else 3
+            barrier()
+            t_local = max_over_ranks(device_time_ms(torch, stream, local, iters))
+            case = {"n_total": n_total, "k": k, "m": m, "rows_per_gpu": n,
+                    "kernel": int(lib.nne_qlinear_kernel_for(h, m)), "kernel_only_us": t_local * 1e3}
+            flops = 2.0 * m * n_total * k
+            nbytes = algorithmic_bytes(n_total, k, m)
+            if world > 1:
+                for route, name in ((0, "peer_stores"), (1, "nccl")):
+                    plans = []
+                    for a in areas:
+                        p = C.c_void_p()
+                        if lib.nne_qlinear_plan_create_sharded(
+                                group.handle, 1, (C.c_void_p * 1)(h), (C.c_size_t * 1)(rank * n),
+                                (C.c_size_t * 1)(n_total), (C.c_void_p * 1)(x.data_ptr()),
+                                (C.c_void_p * 1)(a), m, route, C.byref(p)) != 0:
+                            raise RuntimeError(nne._lib.last_error())
+                        plans.append(p)
+                    turn = [0]
+
+                    def run():
+                        p = plans[turn[0] & 1]
+                        turn[0] += 1
+                        if lib.nne_qlinear_plan_run(p, stream.cuda_stream) != 0:
+                            raise RuntimeError(nne._lib.last_error())
+
+                    barrier()
+                    t = max_over_ranks(device_time_ms(torch, stream, run, iters))
+                    barrier()
+                    ctx.check()
+                    case[name + "_us"] = t * 1e3
+                    # the last run went to area (turn-1)&1: the peer's slice there against a local recomputation
+                    got = torch.as_tensor(nne.DeviceArray(areas[(turn[0] - 1) & 1], (m, n_total)), device=dev)
+                    want = torch.empty(m, n, device=dev, dtype=torch.float32)
+                    if lib.nne_qlinear_forward_dev(h_peer, x.data_ptr(), m, k, want.data_ptr(), stream.cuda_stream) != 0:
+                        raise RuntimeError(nne._lib.last_error())
+                    torch.cuda.synchronize()
+                    same = torch.equal(got[:, peer * n:(peer + 1) * n].contiguous().view(torch.int32),
+                                       want.view(torch.int32))
+                    flag = torch.tensor([1 if same else 0], device=dev)
+                    import torch.distributed as dist
+                    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                    case[name + "_identical"] = bool(int(flag.item()))
+                    for p in plans:
+                        lib.nne_qlinear_plan_destroy(p)
+                    barrier()
+                if not (case["peer_stores_identical"] and case["nccl_identical"]):
+                    if rank == 0:
+                        print(json.dumps({"error": "config 5: gathered output differs", "case": case}))
+                    sys.exit(3)
+            t_best = case.get("peer_stores_us", case["kernel_only_us"]) * 1e-6
+            if m == 1:
+                case["GB/s_kernel_only"] = nbytes / (case["kernel_only_us"] * 1e-6) / 1e9
+                case["GB/s"] = nbytes / t_best / 1e9
+                case["frac_of_measured_hbm_per_gpu"] = case["GB/s"] / world / peaks["hbm_gbs"]
+            else:
+                case["TFLOP/s_kernel_only"] = flops / (case["kernel_only_us"] * 1e-6) / 1e12
+                case["TFLOP/s"] = flops / t_best / 1e12
+                case["frac_of_measured_bf16_per_gpu"] = case["TFLOP/s"] / world / peaks["bf16_tflops"]
+                if world > 1:
+                    # what the exchange must move: every rank receives the other ranks' slices
+                    recv = 4.0 * m * (n_total - n)
+                    case["nvlink_floor_us"] = recv / 770e9 * 1e6
+            cases.append(case)
+        lib.nne_qlinear_destroy(h)
+        if h_peer is not None:
+            lib.nne_qlinear_destroy(h_peer)
+        del x, y_local
+    return {"n_gpus": world, "scaling": "strong", "cases": cases,
+            "note": "us = max over ranks of the device time per forward (+ exchange); GB/s and TFLOP/s are "
+                    "whole-layer figures over that time; nvlink_floor_us = bytes a rank must receive / 770 GB/s"}
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     args = ap.parse_args()

@@ -54,6 +54,7 @@ typedef enum nne_status {
 typedef struct nne_ctx nne_ctx;         /* one per device: streams, staging, SM count   */
 typedef struct nne_qlinear nne_qlinear; /* one device-resident int8 layer               */
 typedef struct nne_plan nne_plan;       /* a fixed list of forwards run as one launch   */
+typedef struct nne_shard_group nne_shard_group; /* one rank's end of a column-shard exchange */
 
 /* ---- status text -------------------------------------------------------------------------- */
 
@@ -207,6 +208,94 @@ NNE_API int nne_qlinear_plan_destroy(nne_plan *plan);
 /* 1 when the whole list runs as one streaming launch, 2 when it runs as pre-pass + small-batch
  * kernel, else the number of layers (each then runs its own forward, of one or two launches). */
 NNE_API int nne_qlinear_plan_launches(const nne_plan *plan);
+
+/* ---- the steps either side of a QLinear in a decoder block ------------------------------------
+ * RMSNorm over the last dimension, y = (x * rrms) * gamma with rrms = 1 / sqrt(mean(x^2) + eps)
+ * (src/nn/norm.rs:141-165, row function :517-577); SwiGLU's element-wise step
+ * out = silu(gate) * up, silu(v) = v / (1 + exp(-v)) (src/models/llama.rs:343-346,
+ * src/tensor/ops.rs:177-179); the residual add out = a + b (src/models/llama.rs:377-392).
+ * Device pointers, asynchronous on `stream`.  fp32, within 1e-5 relative of the reference's
+ * results (the sum of squares is taken in another order).  out may alias an input. */
+NNE_API int nne_rmsnorm_dev(nne_ctx *ctx, const float *x_dev, const float *gamma_dev, float eps,
+                            size_t rows, size_t cols, float *y_dev, void *stream);
+NNE_API int nne_silu_mul_dev(nne_ctx *ctx, const float *gate_dev, const float *up_dev, size_t n,
+                             float *out_dev, void *stream);
+NNE_API int nne_add_dev(nne_ctx *ctx, const float *a_dev, const float *b_dev, size_t n, float *out_dev,
+                        void *stream);
+
+/* A plan whose forwards take those steps in their stride.  Item i computes
+ *     y = layer.forward(x') (+ residual),   x' = x | RMSNorm(x; gamma, eps) | silu(x) * x2,
+ * which is how the QLinears of a LLaMA block meet their neighbours: q/k/v and gate/up read
+ * RMSNorm(h) (src/models/llama.rs:377-392), down reads silu(gate) * up (:343-346), o and down add
+ * the residual stream.  For m <= 2 on streaming shapes the decode kernel applies the transform while
+ * it prepares the activations and adds the residual as it stores, so a chain of such plans never
+ * leaves the device and launches nothing but the forwards; for other shapes the plan runs the
+ * standalone kernels above around its forwards (into buffers it owns).  Results equal the
+ * standalone kernels followed by nne_qlinear_forward_dev bit for bit in the second case and within
+ * 1e-5 relative in the first (rrms is summed in another order). */
+enum { NNE_INPUT_PLAIN = 0, NNE_INPUT_RMSNORM = 1, NNE_INPUT_SILU_MUL = 2 };
+typedef struct nne_plan_item {
+    nne_qlinear *layer;
+    const float *x;        /* [m, in_features] */
+    float *y;              /* [m, out_features] */
+    int input_op;          /* NNE_INPUT_* */
+    float eps;             /* RMSNORM */
+    const float *gamma;    /* RMSNORM: [in_features] */
+    const float *x2;       /* SILU_MUL: [m, in_features] (the "up" half; x is the "gate" half) */
+    const float *residual; /* NULL, or [m, out_features] added to the forward's result */
+} nne_plan_item;
+NNE_API int nne_qlinear_plan_create_fused(nne_ctx *ctx, size_t count, const nne_plan_item *items,
+                                          size_t m, nne_plan **out);
+
+/* ---- column shards over the GPUs of one node -------------------------------------------------
+ * The reference has no multi-device code.  Its forward computes output channel j from row j of
+ * qweight, scales[j] and bias[j] alone (src/nn/quantized.rs:184-192) and quantizes per row
+ * (:107-127), so rank g of G can own the rows [b_g, e_g) of a layer as an ordinary nne_qlinear
+ * (bit-identical codes) and compute columns [b_g, e_g) of y [m, n_total]; every rank then needs all
+ * columns - an all-gather of the output slices.
+ *
+ * A shard group is one rank's end of that exchange: one process per GPU (handles exchanged by any
+ * transport) or one process driving several devices.  It owns a WINDOW of device memory which every
+ * peer maps.  Gathered outputs live at the same offset in every rank's window.  Two routes:
+ *   route 0, peer stores: the decode kernel (m <= 2 on streaming shapes) stores each result into all
+ *            G windows itself; for other shapes a copy kernel pushes the slice out after the local
+ *            forward.  Ordinary stores to peer-mapped memory, arrival counted in the windows, every
+ *            wait bounded (about 2 s, then NNE_ERR_TIMEOUT through nne_cuda_ctx_check).  When a run's
+ *            kernels have finished on a rank, that rank's window holds every rank's slice.
+ *   route 1, NCCL:  ncclAllGather on a communicator the host created (nne_shard_group_set_nccl);
+ *            needs equal slices in rank order.  m = 1 gathers in place; m > 1 gathers [m, width]
+ *            blocks into a staging area and interleaves them into row-major [m, n_total].
+ * Rules, as for collectives: all ranks issue the same sequence of sharded runs on a group, and an
+ * output location must not be the target of two consecutive runs (alternate two areas of the
+ * window), because a rank may begin run e+1 while a peer still reads the result of run e.
+ * A group holds at most 8 ranks.  No multicast object and no TMA access to peer memory is used. */
+#define NNE_SHARD_HANDLE_BYTES 64
+/* Allocates this rank's window of `window_bytes` (zero-filled; cudaMalloc, so it can be exported). */
+NNE_API int nne_shard_group_create(nne_ctx *ctx, int rank, int world, size_t window_bytes,
+                                   nne_shard_group **out);
+/* Writes the NNE_SHARD_HANDLE_BYTES-byte handle other PROCESSES need to map this window. */
+NNE_API int nne_shard_group_handle(const nne_shard_group *group, void *handle_out);
+/* all_handles: world x NNE_SHARD_HANDLE_BYTES bytes in rank order (the own entry is ignored). */
+NNE_API int nne_shard_group_connect(nne_shard_group *group, const void *all_handles);
+/* One process driving all devices: all_groups[p] is rank p's group (peer access is enabled). */
+NNE_API int nne_shard_group_connect_local(nne_shard_group *group, nne_shard_group *const *all_groups);
+/* The window: device pointer and usable size. */
+NNE_API int nne_shard_group_window(const nne_shard_group *group, void **base, size_t *bytes);
+/* ncclComm_t (as void*) of this rank, created by the host, for route 1.  The library calls the
+ * NCCL copy the process has loaded (or the one NNE_NCCL_LIB names); it does not link NCCL. */
+NNE_API int nne_shard_group_set_nccl(nne_shard_group *group, void *nccl_comm);
+NNE_API int nne_shard_group_destroy(nne_shard_group *group);
+/* A plan over column shards: shards[i] holds rows [row_begin[i], row_begin[i] + shards[i].n) of a
+ * layer with n_total[i] output channels; x_dev[i] is [m, k_i] (replicated on every rank, anywhere
+ * in device memory); y_full_dev[i] is the gathered output [m, n_total[i]] INSIDE this rank's window,
+ * at the same window offset on every rank.  nne_qlinear_plan_run runs the forwards and the
+ * exchange; nne_qlinear_plan_run_host returns the gathered outputs (m * n_total[i] floats each).
+ * A group of one rank runs like an ordinary plan.  Destroy with nne_qlinear_plan_destroy. */
+NNE_API int nne_qlinear_plan_create_sharded(nne_shard_group *group, size_t count,
+                                            nne_qlinear *const *shards, const size_t *row_begin,
+                                            const size_t *n_total, const float *const *x_dev,
+                                            float *const *y_full_dev, size_t m, int route,
+                                            nne_plan **out);
 
 /* Which kernel a forward of m rows on this layer dispatches to: 1 = streaming GEMV (small m),
  * 2 = tcgen05/TMEM tensor-core kernel (integer form; NNE_PREFILL=bf16 in the environment selects

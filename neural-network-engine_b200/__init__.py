@@ -8,6 +8,7 @@ from ._lib import NneError, load, LIB_PATH  # noqa: F401
 from .quantized import (  # noqa: F401
     CudaContext,
     EngineError,
+    FusedPlan,
     GpuError,
     Int8Tensor,
     InvalidArgument,
@@ -15,6 +16,22 @@ from .quantized import (  # noqa: F401
     QLinear,
     QLinearPlan,
     ShapeMismatch,
+    add_device,
     default_context,
+    rmsnorm_device,
+    silu_mul_device,
 )
-from .sharding import ShardedQLinear, assemble, shard_rows, shard_sizes  # noqa: F401
+from . import safetensors_int8  # noqa: F401
+from .safetensors_int8 import load_qlinear, save_qlinears  # noqa: F401
+from .sharding import (  # noqa: F401
+    ROUTE_NCCL,
+    ROUTE_PEER_STORES,
+    DeviceArray,
+    NcclComm,
+    ShardGroup,
+    ShardedPlan,
+    ShardedQLinear,
+    assemble,
+    shard_rows,
+    shard_sizes,
+)

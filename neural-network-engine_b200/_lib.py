@@ -68,9 +68,35 @@ SIGNATURES = {
     "nne_qlinear_plan_run_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "nne_qlinear_plan_destroy": (C.c_int, [C.c_void_p]),
     "nne_qlinear_plan_launches": (C.c_int, [C.c_void_p]),
+    "nne_rmsnorm_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_size_t, C.c_size_t,
+                                  C.c_void_p, C.c_void_p]),
+    "nne_silu_mul_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "nne_add_dev": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    "nne_qlinear_plan_create_fused": (C.c_int, [C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, c_void_pp]),
+    "nne_shard_group_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_size_t, c_void_pp]),
+    "nne_shard_group_handle": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "nne_shard_group_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "nne_shard_group_connect_local": (C.c_int, [C.c_void_p, c_void_pp]),
+    "nne_shard_group_window": (C.c_int, [C.c_void_p, c_void_pp, C.POINTER(C.c_size_t)]),
+    "nne_shard_group_set_nccl": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "nne_shard_group_destroy": (C.c_int, [C.c_void_p]),
+    "nne_qlinear_plan_create_sharded": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp,
+                                                  C.POINTER(C.c_size_t), C.POINTER(C.c_size_t),
+                                                  c_void_pp, c_void_pp, C.c_size_t, C.c_int,
+                                                  c_void_pp]),
     "nne_qlinear_kernel_for": (C.c_int, [C.c_void_p, C.c_size_t]),
     "nne_launch_count": (C.c_uint64, []),
 }
+
+
+
+class PlanItem(C.Structure):
+    """nne_plan_item of include/nne_cuda.h."""
+    _fields_ = [("layer", C.c_void_p), ("x", C.c_void_p), ("y", C.c_void_p), ("input_op", C.c_int),
+                ("eps", C.c_float), ("gamma", C.c_void_p), ("x2", C.c_void_p), ("residual", C.c_void_p)]
+
+
+INPUT_PLAIN, INPUT_RMSNORM, INPUT_SILU_MUL = 0, 1, 2
 
 _lib = None
 

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "shard.cuh"
 
 namespace nne {
 
@@ -643,7 +644,193 @@ int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, siz
     NNE_GUARD_END
 }
 
+}  // extern "C"
+
 // ---- plan ---------------------------------------------------------------------------------------
+
+namespace nne {
+namespace {
+
+// Fills the plan's layer lists and decides how it runs (one streaming launch, one small-batch
+// launch, or layer by layer).  y[i] / ldy[i] are where this plan's kernels write.
+int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *layers,
+               const float *const *x_dev_in, float *const *y_dev, const size_t *ldy_or_null, size_t m,
+               const nne_plan_item *items = nullptr) {
+    plan->ctx = ctx;
+    plan->m = m;
+    bool fused = (m >= 1 && m <= 2);
+    // Can the whole list run as one streaming launch?  Then that kernel applies the items' input
+    // transforms and residuals itself.  Otherwise they become standalone launches around the
+    // forwards, and the forwards read the transformed activations from a buffer of the plan.
+    for (size_t i = 0; i < count && fused; ++i) {
+        nne_qlinear *ql = layers[i];
+        NNE_TRY(check_layer(ql));
+        fused = aligned(ql->q, 16) && aligned(x_dev_in[i], 16) && aligned(y_dev[i], 4) &&
+                gemv_tma_supports(ql->n, ql->k, m) &&
+                !(m >= 2 && !skinny_disabled() && ql->tmap_wsk);
+    }
+    std::vector<const float *> x_eff(x_dev_in, x_dev_in + count);
+    if (items && !fused) {
+        size_t floats = 0;
+        for (size_t i = 0; i < count; ++i) {
+            if (items[i].input_op == NNE_INPUT_PLAIN) continue;
+            bool seen = false;
+            for (size_t j = 0; j < i && !seen; ++j)
+                seen = items[j].input_op == items[i].input_op && items[j].x == items[i].x &&
+                       items[j].gamma == items[i].gamma && items[j].x2 == items[i].x2 &&
+                       items[j].eps == items[i].eps && layers[j]->k == layers[i]->k;
+            if (!seen) floats += ((m * layers[i]->k + 63) / 64) * 64;
+        }
+        if (floats) NNE_CUDA_TRY(cudaMalloc(&plan->xform_buf, floats * sizeof(float)));
+        size_t off = 0;
+        for (size_t i = 0; i < count; ++i) {
+            if (items[i].input_op == NNE_INPUT_PLAIN) continue;
+            const float *aux = items[i].input_op == NNE_INPUT_RMSNORM ? items[i].gamma : items[i].x2;
+            float *dst = nullptr;
+            for (const nne_plan::PreOp &op : plan->pre_ops)
+                if (op.kind == items[i].input_op && op.x == items[i].x && op.aux == aux &&
+                    op.eps == items[i].eps && op.cols == layers[i]->k)
+                    dst = op.dst;
+            if (!dst) {
+                dst = plan->xform_buf + off;
+                off += ((m * layers[i]->k + 63) / 64) * 64;
+                plan->pre_ops.push_back({items[i].input_op, items[i].x, aux, items[i].eps, dst, m, layers[i]->k});
+            }
+            x_eff[i] = dst;
+        }
+        for (size_t i = 0; i < count; ++i) {
+            if (!items[i].residual) continue;
+            const size_t ldy = ldy_or_null ? ldy_or_null[i] : layers[i]->n;
+            if (m > 1 && ldy != layers[i]->n)
+                return fail(NNE_ERR_UNSUPPORTED, "layer %zu: a residual on strided rows needs the streaming kernel", i);
+            plan->post_ops.push_back({y_dev[i], items[i].residual, m * layers[i]->n});
+        }
+    }
+    const float *const *x_dev = x_eff.data();
+    fused = (m >= 1 && m <= 2);
+    for (size_t i = 0; i < count; ++i) {
+        nne_qlinear *ql = layers[i];
+        NNE_TRY(check_layer(ql));
+        if (ql->ctx != ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "layer %zu lives on another context", i);
+        if (m && ql->n && (!x_dev[i] || !y_dev[i]))
+            return fail(NNE_ERR_INVALID_ARGUMENT, "null x or y pointer for layer %zu", i);
+        const size_t ldy = ldy_or_null ? ldy_or_null[i] : ql->n;
+        if (ldy < ql->n) return fail(NNE_ERR_INVALID_ARGUMENT, "row stride of layer %zu below its width", i);
+        plan->layers.push_back(ql);
+        plan->x.push_back(x_dev[i]);
+        plan->y.push_back(y_dev[i]);
+        plan->ldy.push_back(ldy);
+        StreamLayer L;
+        L.q = ql->q;
+        L.scales = ql->scales;
+        L.bias = ql->bias;
+        L.x = x_dev[i];
+        L.y = y_dev[i];
+        L.ldy = ldy;
+        L.n = (int)ql->n;
+        L.k = (int)ql->k;
+        L.rw = stream_rows_per_stage(ql->k);
+        if (items && plan->pre_ops.empty() && plan->post_ops.empty()) {
+            L.eps = items[i].eps;
+            L.gamma = items[i].input_op == NNE_INPUT_RMSNORM ? items[i].gamma : nullptr;
+            L.x2 = items[i].input_op == NNE_INPUT_SILU_MUL ? items[i].x2 : nullptr;
+            L.residual = items[i].residual;
+        }
+        plan->descs.push_back(L);
+        fused = fused && aligned(ql->q, 16) && aligned(x_dev[i], 16) && aligned(y_dev[i], 4) &&
+                gemv_tma_supports(ql->n, ql->k, m);
+    }
+    plan->fused = fused && count > 0;
+    if (m >= 2 && !skinny_disabled() && skinny_plan_supports(layers, x_dev, y_dev, count, m)) {
+        NNE_TRY(skinny_plan_create(ctx, layers, x_dev, y_dev, ldy_or_null, count, m, &plan->skinny));
+        plan->fused = false;
+    }
+    if (plan->fused && count > (size_t)STREAM_INLINE_LAYERS) {
+        NNE_CUDA_TRY(cudaMalloc(&plan->descs_dev, count * sizeof(StreamLayer)));
+        NNE_CUDA_TRY(cudaMemcpy(plan->descs_dev, plan->descs.data(), count * sizeof(StreamLayer),
+                                cudaMemcpyHostToDevice));
+    }
+    return NNE_OK;
+}
+
+void plan_free(nne_plan *plan) {
+    if (!plan) return;
+    if (plan->ctx) cudaSetDevice(plan->ctx->device);
+    if (plan->descs_dev) cudaFree(plan->descs_dev);
+    if (plan->xform_buf) cudaFree(plan->xform_buf);
+    if (plan->segs_dev) cudaFree(plan->segs_dev);
+    if (plan->staging) cudaFree(plan->staging);
+    skinny_plan_destroy(plan->skinny);
+    delete plan;
+}
+
+// The plan's forward kernels on `s`, each layer writing y[i] at row stride ldy[i].
+int plan_compute(nne_plan *plan, const PeerSet *peers, cudaStream_t s) {
+    if (plan->fused)
+        return launch_stream_batch(plan->ctx, plan->descs.data(), plan->descs_dev, (int)plan->descs.size(),
+                                   plan->m, false, s, peers);
+    for (const nne_plan::PreOp &op : plan->pre_ops) {
+        if (op.kind == NNE_INPUT_RMSNORM)
+            NNE_TRY(launch_rmsnorm(plan->ctx, op.x, op.aux, op.eps, op.rows, op.cols, op.dst, s));
+        else
+            NNE_TRY(launch_silu_mul(plan->ctx, op.x, op.aux, op.rows * op.cols, op.dst, s));
+    }
+    if (plan->skinny) {
+        NNE_TRY(skinny_plan_run(plan->skinny, s));
+    } else {
+        for (size_t i = 0; i < plan->layers.size(); ++i)
+            NNE_TRY(forward_dev(plan->layers[i], plan->x[i], plan->m, plan->layers[i]->k, plan->y[i],
+                                plan->ldy[i], s));
+    }
+    for (const nne_plan::PostOp &op : plan->post_ops)
+        NNE_TRY(launch_add(plan->ctx, op.y, op.residual, op.count, op.y, s));
+    return NNE_OK;
+}
+
+// One run of a plan: the forwards and, for column shards, the exchange of the output slices.
+int plan_issue(nne_plan *plan, cudaStream_t s) {
+    nne_shard_group *g = plan->group;
+    if (!g || g->world == 1) return plan_compute(plan, nullptr, s);
+    if (!g->connected) return fail(NNE_ERR_INVALID_ARGUMENT, "the shard group is not connected to its peers");
+    if (plan->route == 0) {
+        const unsigned long long epoch = g->epoch.fetch_add(1) + 1;
+        if (plan->fused) {
+            // the streaming kernel stores into every window itself and waits for the others
+            const PeerSet ps = shard_peerset(g, epoch);
+            return plan_compute(plan, &ps, s);
+        }
+        NNE_TRY(plan_compute(plan, nullptr, s));
+        return shard_push(g, plan->segs_dev, (int)plan->layers.size(), plan->push_floats, epoch, s);
+    }
+    // NCCL route.  One row (or a world of one column block each): the slices already sit where an
+    // in-place all-gather of y_full wants them.  More rows: gather [m, width] blocks into a staging
+    // area and interleave them into row-major y_full.
+    const size_t count = plan->layers.size();
+    if (plan->m == 1) {
+        NNE_TRY(plan_compute(plan, nullptr, s));
+        NNE_TRY(shard_nccl_group_start());
+        int st = NNE_OK;
+        for (size_t i = 0; i < count && st == NNE_OK; ++i)
+            st = shard_nccl_all_gather(g, plan->y[i], plan->y_full[i], plan->layers[i]->n, s);
+        const int st2 = shard_nccl_group_end();
+        return st != NNE_OK ? st : st2;
+    }
+    for (size_t i = 0; i < count; ++i) {
+        nne_qlinear *ql = plan->layers[i];
+        const size_t w = ql->n;
+        float *mine = plan->staging + (size_t)g->rank * plan->m * w;
+        NNE_TRY(forward_dev(ql, plan->x[i], plan->m, ql->k, mine, w, s));
+        NNE_TRY(shard_nccl_all_gather(g, mine, plan->staging, plan->m * w, s));
+        NNE_TRY(shard_interleave(plan->ctx, plan->staging, plan->y_full[i], g->world, plan->m, w,
+                                 plan->n_total[i], s));
+    }
+    return NNE_OK;
+}
+
+}  // namespace
+}  // namespace nne
+
+extern "C" {
 
 int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *layers,
                             const float *const *x_dev, float *const *y_dev, size_t m,
@@ -655,49 +842,133 @@ int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *laye
     if (count && (!layers || !x_dev || !y_dev))
         return fail(NNE_ERR_INVALID_ARGUMENT, "null layer / x / y array");
     if (count > 0x7fffffffu) return fail(NNE_ERR_INVALID_ARGUMENT, "too many layers");
-    std::unique_ptr<nne_plan> plan(new nne_plan());
-    plan->ctx = ctx;
-    plan->m = m;
-    bool fused = (m >= 1 && m <= 2);
+    nne_plan *plan = new nne_plan();
+    int st = plan_build(plan, ctx, count, layers, x_dev, y_dev, nullptr, m);
+    if (st != NNE_OK) {
+        plan_free(plan);
+        return st;
+    }
+    *out = plan;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_plan_create_fused(nne_ctx *ctx, size_t count, const nne_plan_item *items, size_t m,
+                                  nne_plan **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    NNE_TRY(use_ctx(ctx));
+    if (count == 0 || count > 0x7fffffffu || !items) return fail(NNE_ERR_INVALID_ARGUMENT, "empty or null item list");
+    std::vector<nne_qlinear *> layers(count);
+    std::vector<const float *> xs(count);
+    std::vector<float *> ys(count);
     for (size_t i = 0; i < count; ++i) {
-        nne_qlinear *ql = layers[i];
-        NNE_TRY(check_layer(ql));
-        if (ql->ctx != ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "layer %zu lives on another context", i);
-        if (m && ql->n && (!x_dev[i] || !y_dev[i]))
-            return fail(NNE_ERR_INVALID_ARGUMENT, "null x or y pointer for layer %zu", i);
-        plan->layers.push_back(ql);
-        plan->x.push_back(x_dev[i]);
-        plan->y.push_back(y_dev[i]);
-        StreamLayer L;
-        L.q = ql->q;
-        L.scales = ql->scales;
-        L.bias = ql->bias;
-        L.x = x_dev[i];
-        L.y = y_dev[i];
-        L.ldy = ql->n;
-        L.n = (int)ql->n;
-        L.k = (int)ql->k;
-        L.rw = stream_rows_per_stage(ql->k);
-        plan->descs.push_back(L);
-        fused = fused && aligned(ql->q, 16) && aligned(x_dev[i], 16) && aligned(y_dev[i], 4) &&
-                gemv_tma_supports(ql->n, ql->k, m);
+        const nne_plan_item &it = items[i];
+        if (it.input_op != NNE_INPUT_PLAIN && it.input_op != NNE_INPUT_RMSNORM && it.input_op != NNE_INPUT_SILU_MUL)
+            return fail(NNE_ERR_INVALID_ARGUMENT, "item %zu: unknown input_op %d", i, it.input_op);
+        if (it.input_op == NNE_INPUT_RMSNORM && !it.gamma)
+            return fail(NNE_ERR_INVALID_ARGUMENT, "item %zu: RMSNorm input needs gamma", i);
+        if (it.input_op == NNE_INPUT_SILU_MUL && !it.x2)
+            return fail(NNE_ERR_INVALID_ARGUMENT, "item %zu: silu(x) * x2 input needs x2", i);
+        NNE_TRY(check_layer(it.layer));
+        if (it.input_op == NNE_INPUT_RMSNORM && it.layer->k == 0)
+            return fail(NNE_ERR_INVALID_ARGUMENT, "item %zu: RMSNorm over an empty dimension", i);
+        layers[i] = it.layer;
+        xs[i] = it.x;
+        ys[i] = it.y;
     }
-    plan->fused = fused && count > 0;
-    if (m >= 2 && !skinny_disabled() && skinny_plan_supports(layers, x_dev, y_dev, count, m)) {
-        NNE_TRY(skinny_plan_create(ctx, layers, x_dev, y_dev, count, m, &plan->skinny));
-        plan->fused = false;
+    nne_plan *plan = new nne_plan();
+    int st = plan_build(plan, ctx, count, layers.data(), xs.data(), ys.data(), nullptr, m, items);
+    if (st != NNE_OK) {
+        cudaGetLastError();
+        plan_free(plan);
+        return st;
     }
-    if (plan->fused && count > (size_t)STREAM_INLINE_LAYERS) {
-        NNE_CUDA_TRY(cudaMalloc(&plan->descs_dev, count * sizeof(StreamLayer)));
-        cudaError_t e = cudaMemcpy(plan->descs_dev, plan->descs.data(), count * sizeof(StreamLayer),
-                                   cudaMemcpyHostToDevice);
-        if (e != cudaSuccess) {
-            cudaFree(plan->descs_dev);
-            skinny_plan_destroy(plan->skinny);
-            return fail(NNE_ERR_CUDA, "plan upload failed: %s", cudaGetErrorString(e));
+    *out = plan;
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_qlinear_plan_create_sharded(nne_shard_group *group, size_t count, nne_qlinear *const *shards,
+                                    const size_t *row_begin, const size_t *n_total,
+                                    const float *const *x_dev, float *const *y_full_dev, size_t m,
+                                    int route, nne_plan **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    if (!group) return fail(NNE_ERR_INVALID_ARGUMENT, "null shard group");
+    nne_ctx *ctx = group->ctx;
+    NNE_TRY(use_ctx(ctx));
+    if (count == 0 || count > 0x7fffffffu || !shards || !row_begin || !n_total || !x_dev || !y_full_dev)
+        return fail(NNE_ERR_INVALID_ARGUMENT, "empty list or null array");
+    if (route != 0 && route != 1) return fail(NNE_ERR_INVALID_ARGUMENT, "route must be 0 (peer stores) or 1 (NCCL)");
+    if (m == 0) return fail(NNE_ERR_INVALID_ARGUMENT, "m must be at least 1");
+    const uint8_t *wbeg = group->base, *wend = group->base + group->flag_off;
+    std::vector<float *> y_slice(count);
+    std::vector<size_t> ldy(count);
+    size_t widest = 0;
+    for (size_t i = 0; i < count; ++i) {
+        NNE_TRY(check_layer(shards[i]));
+        const size_t w = shards[i]->n;
+        size_t t;
+        if (row_begin[i] > n_total[i] || w > n_total[i] - row_begin[i])
+            return fail(NNE_ERR_INVALID_ARGUMENT, "layer %zu: rows [%zu, +%zu) outside %zu output channels", i,
+                        row_begin[i], w, n_total[i]);
+        if (!y_full_dev[i] || mul_overflows(m, n_total[i], &t) || mul_overflows(t, sizeof(float), &t))
+            return fail(NNE_ERR_INVALID_ARGUMENT, "layer %zu: null or oversized output", i);
+        const uint8_t *yb = reinterpret_cast<const uint8_t *>(y_full_dev[i]);
+        if (group->world > 1 && (yb < wbeg || yb + t > wend))
+            return fail(NNE_ERR_INVALID_ARGUMENT,
+                        "layer %zu: the output [m, n_total] must lie inside the group's window", i);
+        if (route == 1 && group->world > 1 &&
+            (w * (size_t)group->world != n_total[i] || row_begin[i] != w * (size_t)group->rank))
+            return fail(NNE_ERR_UNSUPPORTED,
+                        "layer %zu: the NCCL route needs equal slices in rank order (n_total %% world == 0)", i);
+        y_slice[i] = y_full_dev[i] + row_begin[i];
+        ldy[i] = n_total[i];
+        widest = widest > w ? widest : w;
+    }
+    nne_plan *plan = new nne_plan();
+    plan->group = group;
+    plan->route = route;
+    int st = plan_build(plan, ctx, count, shards, x_dev, y_slice.data(), ldy.data(), m);
+    if (st == NNE_OK && group->world > 1) {
+        plan->y_full.assign(y_full_dev, y_full_dev + count);
+        plan->n_total.assign(n_total, n_total + count);
+        plan->row_begin.assign(row_begin, row_begin + count);
+        if (route == 0 && !plan->fused) {
+            std::vector<PushSeg> segs(count);
+            for (size_t i = 0; i < count; ++i) {
+                segs[i].y = y_slice[i];
+                segs[i].ldy = ldy[i];
+                segs[i].rows = (unsigned)m;
+                segs[i].width = (unsigned)shards[i]->n;
+                segs[i].vec = aligned(y_slice[i], 16) && ldy[i] % 4 == 0 && shards[i]->n % 4 == 0;
+                plan->push_floats += m * shards[i]->n;
+            }
+            cudaError_t e = cudaMalloc(&plan->segs_dev, count * sizeof(PushSeg));
+            if (e == cudaSuccess)
+                e = cudaMemcpy(plan->segs_dev, segs.data(), count * sizeof(PushSeg), cudaMemcpyHostToDevice);
+            if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "plan upload failed: %s", cudaGetErrorString(e));
         }
+        if (route == 1 && m > 1) {
+            cudaError_t e = cudaMalloc(&plan->staging, (size_t)group->world * m * widest * sizeof(float));
+            if (e != cudaSuccess)
+                st = fail(e == cudaErrorMemoryAllocation ? NNE_ERR_OUT_OF_MEMORY : NNE_ERR_CUDA,
+                          "staging allocation failed: %s", cudaGetErrorString(e));
+        }
+    } else if (st == NNE_OK) {
+        plan->y_full.assign(y_full_dev, y_full_dev + count);
+        plan->n_total.assign(n_total, n_total + count);
+        plan->row_begin.assign(row_begin, row_begin + count);
     }
-    *out = plan.release();
+    if (st != NNE_OK) {
+        cudaGetLastError();
+        plan_free(plan);
+        return st;
+    }
+    *out = plan;
     return NNE_OK;
     NNE_GUARD_END
 }
@@ -707,15 +978,7 @@ int nne_qlinear_plan_run(nne_plan *plan, void *stream) {
     if (!plan || !plan->ctx) return fail(NNE_ERR_INVALID_ARGUMENT, "null plan");
     if (plan->layers.empty() || plan->m == 0) return NNE_OK;
     NNE_TRY(use_ctx(plan->ctx));
-    cudaStream_t s = (cudaStream_t)stream;
-    if (plan->fused)
-        return launch_stream_batch(plan->ctx, plan->descs.data(), plan->descs_dev,
-                                   (int)plan->descs.size(), plan->m, false, s);
-    if (plan->skinny) return skinny_plan_run(plan->skinny, s);
-    for (size_t i = 0; i < plan->layers.size(); ++i)
-        NNE_TRY(forward_dev(plan->layers[i], plan->x[i], plan->m, plan->layers[i]->k, plan->y[i],
-                            plan->layers[i]->n, s));
-    return NNE_OK;
+    return plan_issue(plan, (cudaStream_t)stream);
     NNE_GUARD_END
 }
 
@@ -729,7 +992,8 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
     std::lock_guard<std::mutex> lock(ctx->mu);
     cudaStream_t s = ctx->stream;
     const size_t count = plan->layers.size();
-    // Neighbouring device buffers that continue one another are moved with one copy.
+    // Neighbouring device buffers that continue one another are moved with one copy; an x
+    // several layers share (same pointer, q/k/v) appears once in x_all_host per layer all the same.
     size_t i = 0, off = 0;
     while (i < count) {
         size_t j = i, len = 0;
@@ -741,22 +1005,18 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
         off += len;
         i = j;
     }
-    if (plan->fused) {
-        NNE_TRY(launch_stream_batch(ctx, plan->descs.data(), plan->descs_dev, (int)plan->descs.size(),
-                                    plan->m, false, s));
-    } else if (plan->skinny) {
-        NNE_TRY(skinny_plan_run(plan->skinny, s));
-    } else {
-        for (size_t l = 0; l < count; ++l)
-            NNE_TRY(forward_dev(plan->layers[l], plan->x[l], plan->m, plan->layers[l]->k, plan->y[l],
-                                plan->layers[l]->n, s));
-    }
+    NNE_TRY(plan_issue(plan, s));
+    // What comes back: y_i [m, n_i], or for column shards the gathered y_full_i [m, n_total_i].
+    const bool sharded = plan->group != nullptr;
     i = 0;
     off = 0;
     while (i < count) {
         size_t j = i, len = 0;
-        float *base = plan->y[i];
-        while (j < count && plan->y[j] == base + len) len += plan->m * plan->layers[j++]->n;
+        float *base = sharded ? plan->y_full[i] : plan->y[i];
+        while (j < count && (sharded ? plan->y_full[j] : plan->y[j]) == base + len) {
+            len += plan->m * (sharded ? plan->n_total[j] : plan->layers[j]->n);
+            ++j;
+        }
         if (len)
             NNE_CUDA_TRY(cudaMemcpyAsync(y_all_host + off, base, len * sizeof(float),
                                          cudaMemcpyDeviceToHost, s));
@@ -776,17 +1036,15 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
 int nne_qlinear_plan_launches(const nne_plan *plan) {
     if (!plan) return 0;
     if (plan->fused) return 1;
-    if (plan->skinny) return 2;  // pre-pass + kernel
-    return (int)plan->layers.size();
+    const int extra = (int)(plan->pre_ops.size() + plan->post_ops.size());
+    const int push = extra + ((plan->group && plan->group->world > 1 && plan->route == 0) ? 1 : 0);  // + slice push kernel
+    if (plan->skinny) return 2 + push;  // pre-pass + kernel
+    return (int)plan->layers.size() + push;
 }
 
 int nne_qlinear_plan_destroy(nne_plan *plan) {
     NNE_GUARD_BEGIN
-    if (!plan) return NNE_OK;
-    if (plan->ctx) cudaSetDevice(plan->ctx->device);
-    if (plan->descs_dev) cudaFree(plan->descs_dev);
-    skinny_plan_destroy(plan->skinny);
-    delete plan;
+    plan_free(plan);
     return NNE_OK;
     NNE_GUARD_END
 }

@@ -155,6 +155,13 @@ struct StreamLayer {
     size_t ldy;
     int n, k;
     int rw;  // weight rows per ring stage: stream_rows_per_stage(k)
+    // What the layer multiplies is x' = x (both null), RMSNorm(x) = (x * rrms) * gamma (gamma set), or
+    // silu(x) * x2 (x2 set, [m, k]); what it writes is forward(x') + residual (residual set, laid out
+    // like y).  The steps either side of a QLinear in a decoder block, done where x and y pass anyway.
+    float eps = 0.0f;
+    const float *gamma = nullptr;
+    const float *x2 = nullptr;
+    const float *residual = nullptr;
 };
 constexpr int STREAM_INLINE_LAYERS = 8;  // descriptors passed in the kernel's parameter block
 struct StreamBatch {
@@ -171,11 +178,17 @@ int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const fl
 int launch_gemv_tma_passes(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                            const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                            cudaStream_t s);
+struct PeerSet;  // shard.cuh: the other ranks' windows, for a column shard's launch
 int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
-                        size_t m, bool reuse, cudaStream_t s);
+                        size_t m, bool reuse, cudaStream_t s, const PeerSet *peers = nullptr);
 int launch_generic(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                    const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                    cudaStream_t s);
+
+int launch_rmsnorm(nne_ctx *ctx, const float *x, const float *gamma, float eps, size_t rows, size_t cols,
+                   float *y, cudaStream_t s);
+int launch_silu_mul(nne_ctx *ctx, const float *gate, const float *up, size_t n, float *out, cudaStream_t s);
+int launch_add(nne_ctx *ctx, const float *a, const float *b, size_t n, float *out, cudaStream_t s);
 
 bool prefill_supports(const nne_qlinear *ql, size_t m);
 int prefill_prepare_layer(nne_qlinear *ql);  // builds the weight TMA descriptor
@@ -190,7 +203,7 @@ struct SkPlan;  // several small-batch forwards as one launch (skinny.cu)
 bool skinny_plan_supports(nne_qlinear *const *layers, const float *const *x, float *const *y,
                           size_t count, size_t m);
 int skinny_plan_create(nne_ctx *ctx, nne_qlinear *const *layers, const float *const *x, float *const *y,
-                       size_t count, size_t m, SkPlan **out);
+                       const size_t *ldy_or_null, size_t count, size_t m, SkPlan **out);
 int skinny_plan_run(SkPlan *plan, cudaStream_t s);
 void skinny_plan_destroy(SkPlan *plan);
 bool prefill_i8_supports(const nne_qlinear *ql, size_t m);
@@ -203,14 +216,46 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
 
 #include <vector>
 
+struct nne_shard_group;
+namespace nne {
+struct PushSeg;
+}
+
 struct nne_plan {
     nne_ctx *ctx = nullptr;
     size_t m = 0;
     bool fused = false;  // the whole list runs as one streaming launch
     std::vector<nne_qlinear *> layers;
     std::vector<const float *> x;
-    std::vector<float *> y;
+    std::vector<float *> y;      // where this plan's kernels write layer i (a shard: its slice of y_full)
+    std::vector<size_t> ldy;     // row stride of y[i] in floats
     std::vector<nne::StreamLayer> descs;
     nne::StreamLayer *descs_dev = nullptr;
-    nne::SkPlan *skinny = nullptr;  // 3 <= m <= 16: the whole list as one small-batch launch
+    nne::SkPlan *skinny = nullptr;  // 2 <= m <= 16: the whole list as one small-batch launch
+    // Input transforms and residual adds (nne_qlinear_plan_create_fused) where the forward kernels
+    // of this plan do not do them themselves: standalone launches before / after, into plan-owned
+    // buffers.  Empty for a streaming plan, whose kernel takes them in its stride.
+    struct PreOp {
+        int kind;  // 1 = RMSNorm, 2 = silu(x) * x2
+        const float *x, *aux;  // aux: gamma or x2
+        float eps;
+        float *dst;
+        size_t rows, cols;
+    };
+    struct PostOp {
+        float *y;
+        const float *residual;
+        size_t count;
+    };
+    std::vector<PreOp> pre_ops;
+    std::vector<PostOp> post_ops;
+    float *xform_buf = nullptr;
+    // column shards (nne_qlinear_plan_create_sharded); group == nullptr for an ordinary plan
+    nne_shard_group *group = nullptr;
+    int route = 0;                    // 0 = peer stores, 1 = NCCL all-gather
+    std::vector<float *> y_full;      // [m, n_total[i]] in this rank's window
+    std::vector<size_t> n_total, row_begin;
+    nne::PushSeg *segs_dev = nullptr; // the slices to copy out when the forward kernels do not do it themselves
+    size_t push_floats = 0;
+    float *staging = nullptr;         // NCCL route, m > 1: [world][m][width] of the widest layer
 };

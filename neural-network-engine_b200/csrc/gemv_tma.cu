@@ -43,6 +43,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "shard.cuh"
 
 namespace nne {
 namespace {
@@ -72,11 +73,24 @@ struct RingBars {
     uint64_t xs_full[2];         // activation buffer b is prepared (count: prep warps)
     uint64_t xs_empty[2];        // every math warp is done with activation buffer b (count: math warps)
     int abort_flag;
+    int done_warps;              // math warps that have stored all their results (column shards only)
     int bad_warp[PREP_WARPS];    // per prep warp: its part of x holds Inf/NaN
     float xmax[PREP_WARPS][2];   // per prep warp and activation row: max |x|
     int bad[2];                  // per buffer: the layer's x holds Inf/NaN
     float unscale[2][2][2];      // per buffer and activation row: dot = integer sum * [0] * [1]
+    float sumsq[2][PREP_WARPS][2];  // RMSNorm input: per layer parity, prep warp and row, sum of x^2
+    float rrms[2][2];            // per buffer and activation row: 1 / sqrt(mean(x^2) + eps)
 };
+
+// Element `col` of row m of the layer's effective input x' (see StreamLayer), from the raw x value.
+__device__ __forceinline__ float input_value(const StreamLayer &L, float xv, int m, size_t col, float rrms) {
+    if (L.gamma) return __fmul_rn(__fmul_rn(xv, rrms), __ldg(L.gamma + col));
+    if (L.x2) {
+        const float s = __fdiv_rn(xv, __fadd_rn(1.0f, expf(-xv)));
+        return __fmul_rn(s, L.x2[(size_t)m * L.k + col]);
+    }
+    return xv;
+}
 
 // Row range of CTA `b` of `g` for a layer of n rows: contiguous, as equal as rows allow.
 __host__ __device__ inline void cta_rows(int n, int b, int g, int &row0, int &cnt) {
@@ -112,12 +126,25 @@ __device__ __forceinline__ void chunk_digits(const float (&xv)[16], float f1, fl
 
 // One stage (RW weight rows in shared memory at `st`) against the digit planes `xs`; the warp's
 // lanes split K.  Writes rows [0, rows) of the stage to y.
-template <int MT, int RW>
+// A result goes to y in this rank's memory and, for a column shard (PEER), to the same place in
+// every other rank's window: plain stores through the peer mappings.
+template <bool PEER>
+__device__ __forceinline__ void store_result(float *p, float val, const PeerSet &ps) {
+    *p = val;
+    if (PEER) {
+#pragma unroll
+        for (int q = 0; q < SHARD_MAX_RANKS; ++q)
+            if (q < ps.world && q != ps.rank)
+                *reinterpret_cast<float *>(reinterpret_cast<char *>(p) + ps.delta[q]) = val;
+    }
+}
+
+template <int MT, int RW, bool PEER>
 __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_t *st,
                                               const uint4 *xs, int kpad, int rows, int jl0,
                                               int row0, const float *unscale, const float *scale_s,
                                               const float *bias_s, bool staged, int lane,
-                                              uint32_t empty_bar) {
+                                              uint32_t empty_bar, const PeerSet &ps) {
     const int k = L.k;
     int acc[RW][MT][3];
 #pragma unroll
@@ -170,16 +197,17 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
         const float sc = staged ? scale_s[jl] : __ldg(L.scales + row0 + jl);
         float val = __fmul_rn(dot, sc);
         if (L.bias) val = __fadd_rn(val, staged ? bias_s[jl] : __ldg(L.bias + row0 + jl));
-        L.y[(size_t)m * L.ldy + row0 + jl] = val;
+        if (L.residual) val = __fadd_rn(val, L.residual[(size_t)m * L.ldy + row0 + jl]);
+        store_result<PEER>(L.y + (size_t)m * L.ldy + row0 + jl, val, ps);
     }
 }
 
 // fp32 loop for activations holding Inf/NaN: exact int8 -> f32, FMA accumulation, so that Inf
 // and NaN propagate as IEEE arithmetic prescribes.  Not a fast path.
-template <int MT>
+template <int MT, bool PEER>
 __device__ __noinline__ void consume_stage_fp32(const StreamLayer &L, const uint8_t *st, int rw,
                                                 int rows, int jl0, int row0, int lane,
-                                                uint32_t empty_bar) {
+                                                uint32_t empty_bar, const PeerSet &ps, const float *rrms) {
     const int k = L.k, chunks = k >> 4;
     for (int r = 0; r < rw; ++r) {
         float facc[MT];
@@ -197,7 +225,8 @@ __device__ __noinline__ void consume_stage_fp32(const StreamLayer &L, const uint
                 for (int m = 0; m < MT; ++m) {
                     const float *xr = L.x + (size_t)m * k + (size_t)c * 16;
 #pragma unroll
-                    for (int v = 0; v < 16; ++v) facc[m] = fmaf(xr[v], wf[v], facc[m]);
+                    for (int v = 0; v < 16; ++v)
+                        facc[m] = fmaf(input_value(L, xr[v], m, (size_t)c * 16 + v, rrms[m]), wf[v], facc[m]);
                 }
             }
         }
@@ -210,7 +239,8 @@ __device__ __noinline__ void consume_stage_fp32(const StreamLayer &L, const uint
                 const int j = row0 + jl0 + r;
                 float val = __fmul_rn(t, L.scales[j]);
                 if (L.bias) val = __fadd_rn(val, L.bias[j]);
-                L.y[(size_t)m * L.ldy + j] = val;
+                if (L.residual) val = __fadd_rn(val, L.residual[(size_t)m * L.ldy + j]);
+                store_result<PEER>(L.y + (size_t)m * L.ldy + j, val, ps);
             }
         }
     }
@@ -225,10 +255,14 @@ __device__ __noinline__ void consume_stage_fp32(const StreamLayer &L, const uint
 // Warp roles: warps 0..7 math (warp w owns ring slot w), warps 8..15 prepare the NEXT layer's
 // activations (digit planes, staged scales) into the other of `num_bufs` buffers while the math
 // warps work on the current layer, the last warp is the producer.
-template <int MT>
+//
+// PEER (column shards): every result is also stored into the other ranks' windows, each CTA
+// signals its arrival there once its math warps are done, and CTA 0's producer lane - idle once
+// the last copy is issued - waits until every rank's results for this run have arrived here.
+template <int MT, bool PEER>
 __global__ void __launch_bounds__(THREADS, 1)
 qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int kpad_max,
-                    int sb_rows, int num_bufs, int *err) {
+                    int sb_rows, int num_bufs, int *err, const PeerSet ps) {
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: ring [num_slots][slot_bytes] | xs [num_bufs][MT][3][kpad_max] uint4 | RingBars |
     //         scale_s[num_bufs][sb_rows] | bias_s[num_bufs][sb_rows]
@@ -254,6 +288,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
             mbar_init(smem_u32(&bars->xs_empty[b]), MATH_WARPS);
         }
         bars->abort_flag = 0;
+        bars->done_warps = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -294,6 +329,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                     }
                 }
             }
+            if (PEER && ok && blockIdx.x == 0) (void)shard_wait_all(ps, abort_flag, err, 0x17);
         }
         return;
     }
@@ -328,7 +364,41 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
             }
             if (li == 0) grid_dependency_wait();  // x may be the previous kernel's output
 
-            // pass 1: max |x| and the Inf/NaN flag per activation row
+            // pass 0 (RMSNorm input only): sum of squares per row -> rrms
+            float rr[MT];
+#pragma unroll
+            for (int m = 0; m < MT; ++m) rr[m] = 1.0f;
+            if (L.gamma) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float acc = 0.0f;
+                    for (int c = ptid; c < chunks; c += PREP_THREADS) {
+                        const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            const float4 t4 = ld_f4_hint(p4 + v, pol_keep);
+                            acc = fmaf(t4.x, t4.x, acc);
+                            acc = fmaf(t4.y, t4.y, acc);
+                            acc = fmaf(t4.z, t4.z, acc);
+                            acc = fmaf(t4.w, t4.w, acc);
+                        }
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (lane == 0) bars->sumsq[li & 1][pwarp][m] = acc;
+                }
+                // sumsq alternates by layer parity, so the previous layer's readers are not disturbed
+                named_bar_sync(1, PREP_THREADS);
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float tot = 0.0f;
+                    for (int w = 0; w < PREP_WARPS; ++w) tot += bars->sumsq[li & 1][w][m];
+                    rr[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)k), L.eps)));
+                }
+            }
+            const bool xform = L.gamma != nullptr || L.x2 != nullptr;
+
+            // pass 1: max |x'| and the Inf/NaN flag per activation row
             float mx[MT];
             int bad = 0;
 #pragma unroll
@@ -338,7 +408,14 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                     const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
 #pragma unroll
                     for (int v = 0; v < 4; ++v) {
-                        const float4 t4 = ld_f4_hint(p4 + v, pol_keep);
+                        float4 t4 = ld_f4_hint(p4 + v, pol_keep);
+                        if (xform) {
+                            const size_t col = (size_t)c * 16 + 4 * v;
+                            t4.x = input_value(L, t4.x, m, col + 0, rr[m]);
+                            t4.y = input_value(L, t4.y, m, col + 1, rr[m]);
+                            t4.z = input_value(L, t4.z, m, col + 2, rr[m]);
+                            t4.w = input_value(L, t4.w, m, col + 3, rr[m]);
+                        }
                         const float a0 = fabsf(t4.x), a1 = fabsf(t4.y), a2 = fabsf(t4.z), a3 = fabsf(t4.w);
                         bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) |
                                !(a2 <= 3.402823466e38f) | !(a3 <= 3.402823466e38f);
@@ -371,7 +448,11 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
             named_bar_sync(1, PREP_THREADS);
             bad = 0;
             for (int w = 0; w < PREP_WARPS; ++w) bad |= bars->bad_warp[w];
-            if (ptid == 0) bars->bad[buf] = bad;
+            if (ptid == 0) {
+                bars->bad[buf] = bad;
+#pragma unroll
+                for (int m = 0; m < MT; ++m) bars->rrms[buf][m] = rr[m];
+            }
 
             if (!bad) {
                 // pass 2: digits of rint(x * 2^e) into shared memory (x is re-read; it is in L1 now)
@@ -399,6 +480,11 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                                 xv[4 * v + 1] = t4.y;
                                 xv[4 * v + 2] = t4.z;
                                 xv[4 * v + 3] = t4.w;
+                            }
+                            if (xform) {
+#pragma unroll
+                                for (int v = 0; v < 16; ++v)
+                                    xv[v] = input_value(L, xv[v], m, (size_t)c * 16 + v, rr[m]);
                             }
                             chunk_digits(xv, f1, f2, o0, o1, o2);
                         }
@@ -449,16 +535,17 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                 const uint8_t *st = ring + (size_t)warp * slot_bytes;
                 const uint32_t empty_bar = smem_u32(&bars->empty[warp]);
                 if (bad) {
-                    consume_stage_fp32<MT>(L, st, L.rw, rows, s * L.rw, row0, lane, empty_bar);
+                    consume_stage_fp32<MT, PEER>(L, st, L.rw, rows, s * L.rw, row0, lane, empty_bar, ps,
+                                                 &bars->rrms[buf][0]);
                 } else if (L.rw == 4) {
-                    consume_stage<MT, 4>(L, st, xs, kpad, rows, s * 4, row0, unscale, scale_s, bias_s,
-                                         staged, lane, empty_bar);
+                    consume_stage<MT, 4, PEER>(L, st, xs, kpad, rows, s * 4, row0, unscale, scale_s, bias_s,
+                                               staged, lane, empty_bar, ps);
                 } else if (L.rw == 2) {
-                    consume_stage<MT, 2>(L, st, xs, kpad, rows, s * 2, row0, unscale, scale_s, bias_s,
-                                         staged, lane, empty_bar);
+                    consume_stage<MT, 2, PEER>(L, st, xs, kpad, rows, s * 2, row0, unscale, scale_s, bias_s,
+                                               staged, lane, empty_bar, ps);
                 } else {
-                    consume_stage<MT, 1>(L, st, xs, kpad, rows, s, row0, unscale, scale_s, bias_s,
-                                         staged, lane, empty_bar);
+                    consume_stage<MT, 1, PEER>(L, st, xs, kpad, rows, s, row0, unscale, scale_s, bias_s,
+                                               staged, lane, empty_bar, ps);
                 }
             }
         }
@@ -467,12 +554,22 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars->xs_empty[buf]));
     }
+    if (PEER) {
+        // The warp's stores to the windows are fenced to system scope before it is counted; the
+        // warp that completes the count fences again (it now stands for all eight) and signals.
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence_system();
+            if (atomicAdd(&bars->done_warps, 1) == MATH_WARPS - 1)
+                shard_signal(ps, (int)blockIdx.x, (int)gridDim.x);
+        }
+    }
 }
 
-template <int MT>
+template <int MT, bool PEER>
 int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot_bytes, int kpad,
-                     int sb_rows, int bufs, size_t smem, int grid, cudaStream_t s) {
-    NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_kernel<MT>, smem));
+                     int sb_rows, int bufs, size_t smem, int grid, const PeerSet &ps, cudaStream_t s) {
+    NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_kernel<MT, PEER>, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)THREADS);
@@ -483,8 +580,8 @@ int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_stream_kernel<MT>, batch, slots, slot_bytes, kpad,
-                                       sb_rows, bufs, ctx->err_word);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_stream_kernel<MT, PEER>, batch, slots, slot_bytes, kpad,
+                                       sb_rows, bufs, ctx->err_word, ps);
     count_launch();
     if (e != cudaSuccess)
         return fail(NNE_ERR_CUDA, "streaming kernel launch failed: %s", cudaGetErrorString(e));
@@ -510,7 +607,7 @@ bool gemv_tma_supports(size_t n, size_t k, size_t m) {
 // Launches the streaming kernel over `count` layers (descriptors in host memory `host`; for more
 // than STREAM_INLINE_LAYERS layers `dev` must hold the same descriptors in device memory).
 int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
-                        size_t m, bool reuse, cudaStream_t s) {
+                        size_t m, bool reuse, cudaStream_t s, const PeerSet *peers) {
     if (count <= 0) return NNE_OK;
     if (count > STREAM_INLINE_LAYERS && !dev)
         return fail(NNE_ERR_INVALID_ARGUMENT, "a batch of %d layers needs device descriptors", count);
@@ -549,9 +646,18 @@ int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer
     if (slots > MAX_SLOTS) slots = MAX_SLOTS;
     if (slots < 2) return fail(NNE_ERR_UNSUPPORTED, "k=%zu leaves no room for a ring", kmax);
     const size_t smem = (size_t)slots * slot_bytes + fixed;
+    if (peers && peers->world > 1) {
+        if (m == 1)
+            return launch_stream_mt<1, true>(ctx, batch, slots, slot_bytes, kpad, sb_rows, bufs, smem, grid,
+                                             *peers, s);
+        return launch_stream_mt<2, true>(ctx, batch, slots, slot_bytes, kpad, sb_rows, bufs, smem, grid,
+                                         *peers, s);
+    }
+    const PeerSet none;
     if (m == 1)
-        return launch_stream_mt<1>(ctx, batch, slots, slot_bytes, kpad, sb_rows, bufs, smem, grid, s);
-    return launch_stream_mt<2>(ctx, batch, slots, slot_bytes, kpad, sb_rows, bufs, smem, grid, s);
+        return launch_stream_mt<1, false>(ctx, batch, slots, slot_bytes, kpad, sb_rows, bufs, smem, grid,
+                                          none, s);
+    return launch_stream_mt<2, false>(ctx, batch, slots, slot_bytes, kpad, sb_rows, bufs, smem, grid, none, s);
 }
 
 int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,

@@ -672,7 +672,7 @@ bool skinny_plan_supports(nne_qlinear *const *layers, const float *const *x, flo
 }
 
 int skinny_plan_create(nne_ctx *ctx, nne_qlinear *const *layers, const float *const *x, float *const *y,
-                       size_t count, size_t m, SkPlan **out) {
+                       const size_t *ldy_or_null, size_t count, size_t m, SkPlan **out) {
     *out = nullptr;
     std::unique_ptr<SkPlan> plan(new SkPlan());
     plan->ctx = ctx;
@@ -730,7 +730,7 @@ int skinny_plan_create(nne_ctx *ctx, nne_qlinear *const *layers, const float *co
     long long unit = 0;
     for (size_t i = 0; i < count; ++i) {
         SkLayer &L = descs[i];
-        sk_fill_layer(L, layers[i], y[i], layers[i]->n);
+        sk_fill_layer(L, layers[i], y[i], ldy_or_null ? ldy_or_null[i] : layers[i]->n);
         L.tmap_x = xmaps[input_of[i]];
         L.unscale = inputs[input_of[i]].unscale;
         L.sums = reinterpret_cast<long long *>(z);

@@ -377,3 +377,59 @@ class QLinearPlan:
             self.close()
         except Exception:
             pass
+
+
+# ---- the steps either side of a QLinear in a decoder block ---------------------------------------
+def rmsnorm_device(ctx: CudaContext, x_ptr: int, gamma_ptr: int, eps: float, rows: int, cols: int,
+                   y_ptr: int, stream: int = 0) -> None:
+    """RMSNorm::forward (src/nn/norm.rs:141-165) on device buffers."""
+    try:
+        check(load().nne_rmsnorm_dev(ctx.handle, x_ptr, gamma_ptr, eps, rows, cols, y_ptr, stream))
+    except NneError as e:
+        _raise_mapped(e)
+
+
+def silu_mul_device(ctx: CudaContext, gate_ptr: int, up_ptr: int, n: int, out_ptr: int, stream: int = 0) -> None:
+    """silu(gate) * up (src/models/llama.rs:343-346) on device buffers."""
+    try:
+        check(load().nne_silu_mul_dev(ctx.handle, gate_ptr, up_ptr, n, out_ptr, stream))
+    except NneError as e:
+        _raise_mapped(e)
+
+
+def add_device(ctx: CudaContext, a_ptr: int, b_ptr: int, n: int, out_ptr: int, stream: int = 0) -> None:
+    """The residual add of a decoder block (src/models/llama.rs:377-392) on device buffers."""
+    try:
+        check(load().nne_add_dev(ctx.handle, a_ptr, b_ptr, n, out_ptr, stream))
+    except NneError as e:
+        _raise_mapped(e)
+
+
+class FusedPlan(QLinearPlan):
+    """`nne_qlinear_plan_create_fused`: forwards that apply RMSNorm or silu(x) * x2 to their input and
+    add a residual to their output.  `items` are dicts with keys layer, x, y and optionally
+    rmsnorm=(gamma_ptr, eps), silu_mul=x2_ptr, residual=ptr (all device pointers)."""
+
+    def __init__(self, items, m: int, ctx: Optional[CudaContext] = None):
+        ctx = ctx or items[0]["layer"]._ctx or default_context()
+        n = len(items)
+        arr = (_lib.PlanItem * n)()
+        for i, it in enumerate(items):
+            arr[i].layer = it["layer"]._live_handle()
+            arr[i].x, arr[i].y = int(it["x"]), int(it["y"])
+            arr[i].input_op, arr[i].eps = _lib.INPUT_PLAIN, 0.0
+            if it.get("rmsnorm") is not None:
+                arr[i].input_op = _lib.INPUT_RMSNORM
+                arr[i].gamma, arr[i].eps = int(it["rmsnorm"][0]), float(it["rmsnorm"][1])
+            elif it.get("silu_mul") is not None:
+                arr[i].input_op = _lib.INPUT_SILU_MUL
+                arr[i].x2 = int(it["silu_mul"])
+            if it.get("residual") is not None:
+                arr[i].residual = int(it["residual"])
+        h = C.c_void_p()
+        try:
+            check(load().nne_qlinear_plan_create_fused(ctx.handle, n, arr, m, C.byref(h)))
+        except NneError as e:
+            _raise_mapped(e)
+        self._h, self._layers, self._ctx = h, [it["layer"] for it in items], ctx
+        self._m = int(m)

@@ -286,3 +286,85 @@ NNE_REF_API float nne_ref_tolerance(const int8_t *qweight, const float *scales, 
     }
     return xinf;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * The element-wise steps either side of a QLinear in a LLaMA block (the "next" rows of the path):
+ * RMSNorm (src/nn/norm.rs:100-180, row function :517-577) and SwiGLU's silu(gate) * up
+ * (src/models/llama.rs:343-346 with RawTensor::silu, src/tensor/ops.rs:177-179).
+ * ---------------------------------------------------------------------------------------- */
+
+/* hsum256, src/nn/norm.rs:412-421: (lo128 + hi128), then (s0+s2, s1+s3), then lane0 + lane1. */
+__attribute__((target("avx2,fma"))) static float ref_hsum256(__m256 v) {
+    __m128 v_high = _mm256_extractf128_ps(v, 1);
+    __m128 v_low = _mm256_castps256_ps128(v);
+    __m128 sum128 = _mm_add_ps(v_low, v_high);
+    __m128 shuf = _mm_movehl_ps(sum128, sum128);
+    __m128 sum64 = _mm_add_ps(sum128, shuf);
+    __m128 shuf2 = _mm_shuffle_ps(sum64, sum64, 1);
+    __m128 sum32 = _mm_add_ss(sum64, shuf2);
+    return _mm_cvtss_f32(sum32);
+}
+
+/* fused_rms_norm_row_avx2, src/nn/norm.rs:539-577: 8 lane accumulators with FMA, hsum, scalar
+ * tail with separate multiply and add, rrms = 1 / sqrt(sum/d + eps), out = (x * rrms) * gamma. */
+__attribute__((target("avx2,fma"))) static void ref_rms_norm_row_avx2(const float *x, const float *gamma,
+                                                                       float eps, size_t d, float *out) {
+    __m256 acc_sq = _mm256_setzero_ps();
+    size_t i = 0;
+    while (i + 8 <= d) {
+        __m256 vx = _mm256_loadu_ps(x + i);
+        acc_sq = _mm256_fmadd_ps(vx, vx, acc_sq);
+        i += 8;
+    }
+    float sum_sq = ref_hsum256(acc_sq);
+    while (i < d) {
+        float v = x[i];
+        float p = v * v;
+        sum_sq = sum_sq + p;
+        i += 1;
+    }
+    float mean_sq = sum_sq / (float)d;
+    float rrms = 1.0f / sqrtf(mean_sq + eps);
+    for (i = 0; i < d; ++i) {
+        float t = x[i] * rrms;
+        out[i] = t * gamma[i];
+    }
+}
+
+/* fused_rms_norm_row, portable branch, src/nn/norm.rs:528-534: left-to-right sum of squares. */
+static void ref_rms_norm_row_scalar(const float *x, const float *gamma, float eps, size_t d, float *out) {
+    float sum_sq = 0.0f;
+    for (size_t i = 0; i < d; ++i) {
+        float p = x[i] * x[i];
+        sum_sq = sum_sq + p;
+    }
+    float mean_sq = sum_sq / (float)d;
+    float rrms = 1.0f / sqrtf(mean_sq + eps);
+    for (size_t i = 0; i < d; ++i) {
+        float t = x[i] * rrms;
+        out[i] = t * gamma[i];
+    }
+}
+
+/* RMSNorm::forward, no-grad fast path (src/nn/norm.rs:141-165): one row function per row.
+ * use_avx2: -1 = detect like the reference (:520), 0 = portable, 1 = AVX2. */
+NNE_REF_API void nne_ref_rms_norm(const float *x, const float *gamma, float eps, size_t rows, size_t d,
+                                  float *out, int use_avx2) {
+    int avx = use_avx2 < 0 ? nne_ref_has_avx2_fma() : use_avx2;
+    for (size_t r = 0; r < rows; ++r) {
+        if (avx)
+            ref_rms_norm_row_avx2(x + r * d, gamma, eps, d, out + r * d);
+        else
+            ref_rms_norm_row_scalar(x + r * d, gamma, eps, d, out + r * d);
+    }
+}
+
+/* SwiGLU's element-wise step (src/models/llama.rs:343-346): silu(gate) * up with
+ * silu(x) = x / (1 + exp(-x)) (src/tensor/ops.rs:177-179). */
+NNE_REF_API void nne_ref_silu_mul(const float *gate, const float *up, size_t n, float *out) {
+    for (size_t i = 0; i < n; ++i) {
+        float g = gate[i];
+        float s = g / (1.0f + expf(-g));
+        out[i] = s * up[i];
+    }
+}

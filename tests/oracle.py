@@ -53,6 +53,10 @@ def lib() -> C.CDLL:
         l.nne_ref_forward_f64.restype = None
         l.nne_ref_tolerance.argtypes = [vp, vp, sz, sz, vp, sz, vp]
         l.nne_ref_tolerance.restype = C.c_float
+        l.nne_ref_rms_norm.argtypes = [vp, vp, C.c_float, sz, sz, vp, C.c_int]
+        l.nne_ref_rms_norm.restype = None
+        l.nne_ref_silu_mul.argtypes = [vp, vp, sz, vp]
+        l.nne_ref_silu_mul.restype = None
         _lib = l
     return _lib
 
@@ -139,6 +143,25 @@ def tolerance(q, scales, x):
     return tol, float(xinf)
 
 
+def rms_norm(x, gamma, eps: float = 1e-6, use_avx2: int = -1) -> np.ndarray:
+    """RMSNorm::forward (src/nn/norm.rs:141-165) over the last dimension."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    d = x.shape[-1]
+    out = np.empty_like(x)
+    g = np.ascontiguousarray(gamma, dtype=np.float32)
+    lib().nne_ref_rms_norm(_p(x), _p(g), eps, x.size // d if d else 0, d, _p(out), use_avx2)
+    return out
+
+
+def silu_mul(gate, up) -> np.ndarray:
+    """silu(gate) * up, the element-wise step of SwiGLU (src/models/llama.rs:343-346)."""
+    g = np.ascontiguousarray(gate, dtype=np.float32)
+    u = np.ascontiguousarray(up, dtype=np.float32)
+    out = np.empty_like(g)
+    lib().nne_ref_silu_mul(_p(g), _p(u), g.size, _p(out))
+    return out
+
+
 # ---- independent numpy restatement of the quantize step (src/nn/quantized.rs:107-127) ---------
 def numpy_quantize_rows(w: np.ndarray):
     """Written separately from the C oracle: f32 ops in numpy, the half-away rounding done in
@@ -155,3 +178,62 @@ def numpy_quantize_rows(w: np.ndarray):
         r = np.sign(t64) * np.floor(np.abs(t64) + 0.5)
         r = np.where(np.isnan(r), 0.0, np.clip(r, -128.0, 127.0))
     return r.astype(np.int8), scale
+
+
+# ---- independent numpy restatement of the forward's AVX2 dot product ---------------------------
+def _fma_f32(a: np.ndarray, b: np.ndarray, c: np.ndarray) -> np.ndarray:
+    """Correctly rounded f32 fused multiply-add, element-wise, without an FMA instruction: the
+    product of two f32 is exact in f64; the f64 sum with c is taken with its rounding error
+    (TwoSum) and, when inexact, moved to the neighbour with an odd last bit ("round to odd"), after
+    which the rounding to f32 is the rounding of the exact value (f64 has more than two spare bits)."""
+    p = a.astype(np.float64) * b.astype(np.float64)
+    c64 = c.astype(np.float64)
+    with np.errstate(over="ignore", invalid="ignore"):
+        s = p + c64
+        bb = s - p
+        err = (p - (s - bb)) + (c64 - bb)
+        inexact = np.isfinite(s) & (err != 0)
+        even = (s.view(np.int64) & 1) == 0
+        toward = np.where(err > 0, np.inf, -np.inf)
+        s = np.where(inexact & even, np.nextafter(s, toward), s)
+        return s.astype(np.float32)
+
+
+def numpy_dot_f32_i8_avx2(x: np.ndarray, w: np.ndarray) -> np.float32:
+    """dot_f32_i8_avx2 (src/nn/quantized.rs:276-324), written from the Rust source and not from the
+    C oracle: element i of a 16-block goes to lane i % 16 of two 8-lane accumulators updated by
+    fmadd (:299-300); then acc0 + acc1 (:305), low half + high half (:308-310), the pairwise
+    movehdup / movehl sums (:311-314) and the scalar tail with a separate multiply and add (:318-321)."""
+    x = np.asarray(x, dtype=np.float32)
+    wf = np.asarray(w, dtype=np.int8).astype(np.float32)          # cvtepi8_epi32 + cvtepi32_ps: exact
+    n = x.size
+    blocks = n // 16
+    acc = np.zeros(16, dtype=np.float32)                          # lanes 0-7: acc0, lanes 8-15: acc1
+    xb = x[:blocks * 16].reshape(blocks, 16)
+    wb = wf[:blocks * 16].reshape(blocks, 16)
+    for b in range(blocks):
+        acc = _fma_f32(xb[b], wb[b], acc)
+    a8 = acc[:8] + acc[8:]                                         # _mm256_add_ps(acc0, acc1)
+    s4 = a8[:4] + a8[4:]                                           # lo128 + hi128
+    sums0 = s4[0] + s4[1]                                          # sum128 + movehdup: lanes 0 and 2
+    sums2 = s4[2] + s4[3]
+    total = np.float32(sums0 + sums2)                              # add_ss(sums, movehl(sums, sums))
+    for i in range(blocks * 16, n):
+        total = np.float32(total + np.float32(x[i] * wf[i]))
+    return total
+
+
+def numpy_forward_avx2(q, scales, bias, x) -> np.ndarray:
+    """QLinear::forward_quantized (src/nn/quantized.rs:176-193) over numpy_dot_f32_i8_avx2: dot, then
+    val = dot * scale, then val += bias as separate f32 operations.  Small cases only (Python loops)."""
+    q = np.asarray(q, dtype=np.int8)
+    x = np.asarray(x, dtype=np.float32).reshape(-1, q.shape[1])
+    s = np.asarray(scales, dtype=np.float32)
+    y = np.empty((x.shape[0], q.shape[0]), dtype=np.float32)
+    for r in range(x.shape[0]):
+        for j in range(q.shape[0]):
+            val = np.float32(numpy_dot_f32_i8_avx2(x[r], q[j]) * s[j])
+            if bias is not None:
+                val = np.float32(val + np.float32(bias[j]))
+            y[r, j] = val
+    return y

@@ -82,3 +82,24 @@ def test_example16_layer(nne, ctx):
     a, b = linear_forward_f32(linear, x), q.forward(x)
     cos = float((a * b).sum() / (np.linalg.norm(a) * np.linalg.norm(b)))
     assert cos > 0.999
+
+
+def test_qlinear_saved_as_int8_loads_straight_onto_the_device(nne, ctx, tmp_path):
+    """The int8 on-disk format: a QLinear saved with I8 codes + F32 scales/bias comes back through
+    nne_qlinear_create_from_i8 with identical fields and an identical forward (nothing re-quantized)."""
+    w = oracle.normal(60, 0, (192, 320), 0.0, 0.02)
+    b = oracle.normal(60, 1, (192,), 0.0, 0.1)
+    ql = nne.QLinear.from_linear(nne.Linear(w, b), ctx)
+    nb = nne.QLinear.from_linear(nne.Linear(w[:64], None), ctx)
+    path = str(tmp_path / "layers.safetensors")
+    nne.save_qlinears({"blk.0.up_proj": ql, "blk.0.gate_proj": nb}, path)
+    back = nne.load_qlinear(path, "blk.0.up_proj", ctx)
+    assert np.array_equal(back.qweight, ql.qweight) and np.array_equal(back.scales.view(np.uint32), ql.scales.view(np.uint32))
+    assert np.array_equal(back.bias.view(np.uint32), ql.bias.view(np.uint32))
+    back_nb = nne.load_qlinear(path, "blk.0.gate_proj", ctx)
+    assert back_nb.bias is None
+    for m in (1, 5, 40):
+        x = oracle.normal(61, m, (m, 320))
+        assert np.array_equal(back.forward(x).view(np.uint32), ql.forward(x).view(np.uint32))
+        assert np.array_equal(back_nb.forward(x).view(np.uint32), nb.forward(x).view(np.uint32))
+    ctx.check()
