@@ -277,7 +277,7 @@ def run_native(args):
     route_names = {0: "peer stores from the forward kernel", 1: "ncclAllGather"}
     head_route = 1 if os.environ.get("NNE_BENCH_ROUTE", "").startswith("n") else 0
     if world > 1:
-        window = 4 * (4 * world * y_total + 2 * CONFIG5_M * sum(n for n, _ in CONFIG5_SHAPES)) + (64 << 20)
+        window = 4 * (12 * world * y_total + 2 * CONFIG5_M * sum(n for n, _ in CONFIG5_SHAPES)) + (64 << 20)
         group = nne.ShardGroup(ctx, rank, world, window)
         group.use_nccl()
     layers = []
@@ -292,11 +292,16 @@ def run_native(args):
     xs = (C.c_void_p * nl)(*[L["x"].data_ptr() for L in layers])
 
     # The step as ONE launch: a plan over the whole rotation set.  One GPU: an ordinary plan.
-    # N > 1: sharded plans over two output areas of the window that alternate from step to step
-    # (a rank may begin step i+1 while a peer still reads the result of step i).
-    def sharded_plans(route, x_ptrs=None):
+    # N > 1: sharded plans over AREAS output areas of the window, used in turn.  A run never waits
+    # for another rank: the kernel stores its results into every rank's window and announces the
+    # rank's previous run; the timed region ends with nne_shard_group_wait, after which every rank
+    # holds every slice of every step.  Nothing reads the gathered outputs inside the timed region,
+    # so the areas only keep consecutive steps from writing the same addresses.
+    AREAS = 4
+
+    def sharded_plans(route, x_ptrs=None, count=AREAS):
         plans, areas = [], []
-        for _ in range(2):
+        for _ in range(count):
             base = group.alloc(world * y_total)
             ptrs, off = [], 0
             for L in layers:
@@ -326,19 +331,27 @@ def run_native(args):
         plans, areas = [local_plan], None
     launches_per_step = lib.nne_qlinear_plan_launches(plans[0])
 
-    def stepper(plan_list):
+    def stepper(plan_list, wait=False):
+        """Runs the plans in turn on the main stream.  Peer-store route: a run only stores; each run
+        announces its predecessor from inside the kernel, and `drain` (nne_shard_group_wait)
+        completes the exchange of everything issued so far."""
         turn = [0]
 
         def step():
-            p = plan_list[turn[0] % len(plan_list)]
+            ok(lib.nne_qlinear_plan_run(plan_list[turn[0] % len(plan_list)], stream.cuda_stream))
             turn[0] += 1
-            ok(lib.nne_qlinear_plan_run(p, stream.cuda_stream))
+
+        def drain():
+            if wait:
+                ok(lib.nne_shard_group_wait(group.handle, stream.cuda_stream))
+        step.drain = drain
         return step
 
-    step = stepper(plans)
+    step = stepper(plans, wait=(world > 1 and head_route == 0))
     R = REPEATS_PER_STEP
     for _ in range(max(args.warmup, 3)):
         step()
+    step.drain()
     barrier()
 
     # device-timed region: K steps of R plan launches each, back to back on one stream
@@ -354,6 +367,7 @@ def run_native(args):
     for _ in range(args.steps * R):
         step()
     host_us_per_launch = (time.perf_counter() - h0) * 1e6 / (args.steps * R)  # enqueue only
+    step.drain()  # the last runs' slices have arrived on this rank too
     e1.record(stream)
     barrier()
     launches = lib.nne_launch_count() - launches0
@@ -376,9 +390,24 @@ def run_native(args):
         t_local = max_over_ranks(device_time_ms(torch, stream, stepper([local_plan]), iters))
         barrier()
         other = 1 - head_route
-        t_other = max_over_ranks(device_time_ms(torch, stream, stepper(plans_by_route[other][0]), iters))
+        st_other = stepper(plans_by_route[other][0], wait=(other == 0))
+
+        def other_step():
+            st_other()
+        t_other = max_over_ranks(device_time_ms(torch, stream, other_step, iters))
+        st_other.drain()
+        barrier()
+        serial_turn = [0]
+
+        def serial_step():
+            pl = plans_by_route[0][0]
+            ok(lib.nne_qlinear_plan_run(pl[serial_turn[0] % len(pl)], stream.cuda_stream))
+            ok(lib.nne_shard_group_wait(group.handle, stream.cuda_stream))
+            serial_turn[0] += 1
+        t_serial = max_over_ranks(device_time_ms(torch, stream, serial_step, iters))
         barrier()
         multi = {"kernel_only_us_per_step": t_local * 1e3,
+                 "peer_stores_run_then_wait_in_one_stream_us_per_step": t_serial * 1e3,
                  "kernel_plus_exchange_us_per_step": ms * 1e3 / passes,
                  "route": route_names[head_route],
                  "other_route": {"route": route_names[other], "us_per_step": t_other * 1e3,
@@ -392,6 +421,7 @@ def run_native(args):
             pl, ar = plans_by_route[route]
             barrier()
             ok(lib.nne_qlinear_plan_run(pl[0], stream.cuda_stream))
+            ok(lib.nne_shard_group_wait(group.handle, stream.cuda_stream))
             barrier()
             ctx.check()
             for i in (0, 1, 2):
@@ -460,7 +490,7 @@ def run_native(args):
         xo += L["k"]
     xps_c = (C.c_void_p * nl)(*xps)
     if world > 1:
-        hplans, _ = sharded_plans(head_route, xps_c)
+        hplans, _ = sharded_plans(head_route, xps_c, count=2)
     else:
         yslab = torch.empty(y_total, device=dev, dtype=torch.float32)
         yps, yo = [], 0
@@ -552,7 +582,9 @@ def run_native(args):
                        "weight_bytes_per_pass_per_gpu": sum(L["n"] * L["k"] for L in layers),
                        "l2": "rotation set of distinct weights larger than the 126 MB L2",
                        "parallelism": "1 GPU" if world == 1 else
-                       f"column shards over {world} GPUs, output slices exchanged by {route_names[head_route]}"},
+                       f"column shards over {world} GPUs, output slices exchanged by {route_names[head_route]}"
+                       + ("; steps back to back, one wait for all arrivals closes the timed region"
+                          if head_route == 0 else "")},
             "roofline": {"bound": "hbm", "kernel": "qgemv_stream_kernel", "achieved": achieved,
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
@@ -871,9 +903,13 @@ def run_config5(nne, lib, ctx, dev, group, rank, world, make_layer, peaks, args,
                     turn = [0]
 
                     def run():
+                        # run, then the arrival wait on the same stream: what a consumer of the
+                        # gathered output sees (nothing is overlapped with the next forward)
                         p = plans[turn[0] & 1]
                         turn[0] += 1
                         if lib.nne_qlinear_plan_run(p, stream.cuda_stream) != 0:
+                            raise RuntimeError(nne._lib.last_error())
+                        if route == 0 and lib.nne_shard_group_wait(group.handle, stream.cuda_stream) != 0:
                             raise RuntimeError(nne._lib.last_error())
 
                     barrier()

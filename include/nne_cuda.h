@@ -78,6 +78,13 @@ NNE_API int nne_cuda_ctx_destroy(nne_ctx *ctx);
  * NNE_ERR_TIMEOUT (and clears the word) if that happened since the last check, else NNE_OK.  The
  * `_host` entry points perform this check themselves. */
 NNE_API int nne_cuda_ctx_check(nne_ctx *ctx);
+/* Exercises the path from a wait that runs out to NNE_ERR_TIMEOUT without breaking anything: runs a
+ * one-CTA kernel that waits, with a limit of `limit_us` microseconds, for an event that never
+ * comes (which = 0: a shared-memory barrier nobody arrives at; which = 1: an arrival word of the
+ * column-shard exchange that nothing raises).  The kernel gives up, sets the error word and
+ * returns; the call returns NNE_OK, and the next nne_cuda_ctx_check reports NNE_ERR_TIMEOUT once.
+ * The context stays usable.  No counterpart in the reference. */
+NNE_API int nne_cuda_ctx_selftest_wait(nne_ctx *ctx, int which, unsigned int limit_us);
 /* The streaming GEMV (m <= 2, and every plan it runs) is a persistent kernel with one CTA per SM;
  * a kernel of another library launched beside it (an NCCL collective on a second stream) finds no
  * SM with room for its CTAs and waits for it to end.  This leaves `count` SMs out of that kernel's
@@ -86,6 +93,20 @@ NNE_API int nne_cuda_ctx_reserve_sms(nne_ctx *ctx, int count);
 /* Device facts the host side sizes its work with.  Any out pointer may be NULL. */
 NNE_API int nne_cuda_ctx_info(const nne_ctx *ctx, int *device, int *sm_count, int *cc_major,
                               int *cc_minor, size_t *total_mem_bytes);
+
+/* ---- device buffers -------------------------------------------------------------------------
+ * What a device tensor type on the host side needs, so that a stack of QLinears keeps its
+ * activations on the GPU between layers: the counterparts of GpuTensor::from_slice's buffer and
+ * queue.write_buffer (src/gpu/tensor.rs:19-44) and of GpuTensor::to_cpu (src/gpu/tensor.rs:53-95).
+ * upload returns when the bytes are on the device; download first waits for ALL work issued on the
+ * device (like to_cpu's device.poll(Wait)) and reports a timed-out kernel as NNE_ERR_TIMEOUT. */
+NNE_API int nne_device_alloc(nne_ctx *ctx, size_t bytes, void **out_dev);
+NNE_API int nne_device_free(nne_ctx *ctx, void *ptr_dev);
+NNE_API int nne_device_upload(nne_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+NNE_API int nne_device_download(nne_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
+/* The context's own stream (a cudaStream_t as void*), the one the *_host entry points use: device
+ * forwards issued on it are ordered with them and with each other. */
+NNE_API void *nne_cuda_ctx_stream(nne_ctx *ctx);
 
 /* ---- quantize / dequantize ----------------------------------------------------------------
  * nne_quantize_rows replaces the row loop of QLinear::from_linear (src/nn/quantized.rs:107-127):
@@ -257,17 +278,26 @@ NNE_API int nne_qlinear_plan_create_fused(nne_ctx *ctx, size_t count, const nne_
  * A shard group is one rank's end of that exchange: one process per GPU (handles exchanged by any
  * transport) or one process driving several devices.  It owns a WINDOW of device memory which every
  * peer maps.  Gathered outputs live at the same offset in every rank's window.  Two routes:
- *   route 0, peer stores: the decode kernel (m <= 2 on streaming shapes) stores each result into all
- *            G windows itself; for other shapes a copy kernel pushes the slice out after the local
- *            forward.  Ordinary stores to peer-mapped memory, arrival counted in the windows, every
- *            wait bounded (about 2 s, then NNE_ERR_TIMEOUT through nne_cuda_ctx_check).  When a run's
- *            kernels have finished on a rank, that rank's window holds every rank's slice.
- *   route 1, NCCL:  ncclAllGather on a communicator the host created (nne_shard_group_set_nccl);
- *            needs equal slices in rank order.  m = 1 gathers in place; m > 1 gathers [m, width]
- *            blocks into a staging area and interleaves them into row-major [m, n_total].
- * Rules, as for collectives: all ranks issue the same sequence of sharded runs on a group, and an
- * output location must not be the target of two consecutive runs (alternate two areas of the
- * window), because a rank may begin run e+1 while a peer still reads the result of run e.
+ *   route 0, peer stores: a split-phase exchange.  nne_qlinear_plan_run only produces: the decode
+ *            kernel (m <= 2 on streaming shapes) stores each result into all G windows itself; for
+ *            other shapes a copy kernel pushes the slice out after the local forward.  Ordinary
+ *            stores to peer-mapped memory; the run neither announces itself nor waits for anybody.
+ *            nne_shard_group_wait completes it: it enqueues a one-warp kernel that announces this
+ *            rank's runs issued so far in every window and returns once every rank has announced as
+ *            many, i.e. once this rank's window holds every slice (bounded: about 2 s, then
+ *            NNE_ERR_TIMEOUT through nne_cuda_ctx_check).  EVERY rank must call it for its runs - a
+ *            rank that does not is never heard of.  Put it on a stream ordered after the runs:
+ *            the run's own stream, before the reader of the gathered output; or a second stream
+ *            (after an event), where it overlaps the next run.  nne_qlinear_plan_run_host does run,
+ *            wait and copy-back itself.
+ *   route 1, NCCL:  ncclAllGather on a communicator the host created (nne_shard_group_set_nccl),
+ *            on the run's stream; needs equal slices in rank order.  m = 1 gathers in place; m > 1
+ *            gathers [m, width] blocks into a staging area and interleaves them into row-major
+ *            [m, n_total].  nne_shard_group_wait is not needed (and harmless).
+ * Rules, as for collectives: all ranks issue the same sequence of sharded runs on a group.  A rank
+ * may overwrite an output area only when every peer has finished reading what it held: with run,
+ * wait and the reads in ONE stream two alternating areas are enough ("a peer has signalled run e+1"
+ * implies "it has read run e"); a caller that keeps d runs in flight before it waits needs 2 d areas.
  * A group holds at most 8 ranks.  No multicast object and no TMA access to peer memory is used. */
 #define NNE_SHARD_HANDLE_BYTES 64
 /* Allocates this rank's window of `window_bytes` (zero-filled; cudaMalloc, so it can be exported). */
@@ -281,6 +311,8 @@ NNE_API int nne_shard_group_connect(nne_shard_group *group, const void *all_hand
 NNE_API int nne_shard_group_connect_local(nne_shard_group *group, nne_shard_group *const *all_groups);
 /* The window: device pointer and usable size. */
 NNE_API int nne_shard_group_window(const nne_shard_group *group, void **base, size_t *bytes);
+/* Completes every sharded run issued on this group so far (route 0): announce, then wait. */
+NNE_API int nne_shard_group_wait(nne_shard_group *group, void *stream);
 /* ncclComm_t (as void*) of this rank, created by the host, for route 1.  The library calls the
  * NCCL copy the process has loaded (or the one NNE_NCCL_LIB names); it does not link NCCL. */
 NNE_API int nne_shard_group_set_nccl(nne_shard_group *group, void *nccl_comm);

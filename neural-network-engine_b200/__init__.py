@@ -7,6 +7,8 @@ the CPU and nothing falls back when the library or a GPU is missing.
 from ._lib import NneError, load, LIB_PATH  # noqa: F401
 from .quantized import (  # noqa: F401
     CudaContext,
+    CudaQLinear,
+    CudaTensor,
     EngineError,
     FusedPlan,
     GpuError,

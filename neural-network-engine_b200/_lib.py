@@ -25,6 +25,12 @@ SIGNATURES = {
     "nne_cuda_ctx_create": (C.c_int, [C.c_int, c_void_pp]),
     "nne_cuda_ctx_destroy": (C.c_int, [C.c_void_p]),
     "nne_cuda_ctx_check": (C.c_int, [C.c_void_p]),
+    "nne_device_alloc": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp]),
+    "nne_device_free": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "nne_device_upload": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "nne_device_download": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "nne_cuda_ctx_stream": (C.c_void_p, [C.c_void_p]),
+    "nne_cuda_ctx_selftest_wait": (C.c_int, [C.c_void_p, C.c_int, C.c_uint]),
     "nne_cuda_ctx_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int),
                                     C.POINTER(C.c_int), C.POINTER(C.c_int),
                                     C.POINTER(C.c_size_t)]),
@@ -78,6 +84,7 @@ SIGNATURES = {
     "nne_shard_group_connect": (C.c_int, [C.c_void_p, C.c_void_p]),
     "nne_shard_group_connect_local": (C.c_int, [C.c_void_p, c_void_pp]),
     "nne_shard_group_window": (C.c_int, [C.c_void_p, c_void_pp, C.POINTER(C.c_size_t)]),
+    "nne_shard_group_wait": (C.c_int, [C.c_void_p, C.c_void_p]),
     "nne_shard_group_set_nccl": (C.c_int, [C.c_void_p, C.c_void_p]),
     "nne_shard_group_destroy": (C.c_int, [C.c_void_p]),
     "nne_qlinear_plan_create_sharded": (C.c_int, [C.c_void_p, C.c_size_t, c_void_pp,

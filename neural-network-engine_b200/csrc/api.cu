@@ -308,6 +308,60 @@ int nne_cuda_ctx_info(const nne_ctx *ctx, int *device, int *sm_count, int *cc_ma
     return NNE_OK;
 }
 
+// ---- device buffers for a host-side tensor type ------------------------------------------------
+
+int nne_device_alloc(nne_ctx *ctx, size_t bytes, void **out) {
+    NNE_GUARD_BEGIN
+    if (!out) return fail(NNE_ERR_INVALID_ARGUMENT, "null out pointer");
+    *out = nullptr;
+    NNE_TRY(use_ctx(ctx));
+    NNE_CUDA_TRY(cudaMalloc(out, bytes ? bytes : 1));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_device_free(nne_ctx *ctx, void *ptr) {
+    NNE_GUARD_BEGIN
+    if (!ptr) return NNE_OK;
+    NNE_TRY(use_ctx(ctx));
+    NNE_CUDA_TRY(cudaFree(ptr));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_device_upload(nne_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    if (bytes == 0) return NNE_OK;
+    if (!dst_dev || !src_host) return fail(NNE_ERR_INVALID_ARGUMENT, "null pointer");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    NNE_CUDA_TRY(cudaMemcpyAsync(dst_dev, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    NNE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+int nne_device_download(nne_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    if (bytes == 0) return NNE_OK;
+    if (!dst_host || !src_dev) return fail(NNE_ERR_INVALID_ARGUMENT, "null pointer");
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    // everything issued on the device so far (any stream) is complete before the copy reads
+    NNE_CUDA_TRY(cudaDeviceSynchronize());
+    NNE_CUDA_TRY(cudaMemcpyAsync(dst_host, src_dev, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    NNE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    const int word = *ctx->err_host;
+    if (word != 0) {
+        *ctx->err_host = 0;
+        return fail(NNE_ERR_TIMEOUT, "a kernel's bounded wait ran out (code 0x%x)", word);
+    }
+    return NNE_OK;
+    NNE_GUARD_END
+}
+
+void *nne_cuda_ctx_stream(nne_ctx *ctx) { return ctx ? (void *)ctx->stream : nullptr; }
+
 // ---- quantize ---------------------------------------------------------------------------------
 
 int nne_quantize_rows_dev(nne_ctx *ctx, const float *w_dev, size_t rows, size_t cols, int8_t *q_dev,
@@ -795,7 +849,7 @@ int plan_issue(nne_plan *plan, cudaStream_t s) {
     if (plan->route == 0) {
         const unsigned long long epoch = g->epoch.fetch_add(1) + 1;
         if (plan->fused) {
-            // the streaming kernel stores into every window itself and waits for the others
+            // the streaming kernel stores into every window itself
             const PeerSet ps = shard_peerset(g, epoch);
             return plan_compute(plan, &ps, s);
         }
@@ -1006,6 +1060,7 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
         i = j;
     }
     NNE_TRY(plan_issue(plan, s));
+    if (plan->group && plan->route == 0) NNE_TRY(shard_wait(plan->group, plan->group->epoch.load(), s));
     // What comes back: y_i [m, n_i], or for column shards the gathered y_full_i [m, n_total_i].
     const bool sharded = plan->group != nullptr;
     i = 0;

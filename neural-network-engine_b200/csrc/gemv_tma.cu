@@ -26,10 +26,11 @@
 //
 // Work split: math warp w is bound to ring slot w and takes the stages that land there (a stage =
 // 1-4 weight rows).  Its 32 lanes split K in 16-byte chunks; the integer sums are reduced with
-// redux.sync.  Four more warps prepare the digit planes of the NEXT layer's activations (and stage
+// redux.sync.  Seven more warps prepare the digit planes of the NEXT layer's activations (and stage
 // its scales and bias) into the second of two shared buffers meanwhile, so at a layer boundary
 // neither the math warps nor the weight stream wait for activations.  No CTA-wide barrier: every
-// warp free-runs between mbarriers.
+// warp free-runs between mbarriers.  Sixteen warps in all, four per SM sub-partition, which is what
+// lets every thread have 128 registers (a seventeenth warp would cap them at 96 and spill).
 //
 // The kernel is launched with programmatic stream serialization: its producer starts filling
 // the ring with WEIGHTS while the previous kernel in the stream is still draining, and only
@@ -37,7 +38,7 @@
 // are immutable once a layer exists, which is what makes that early read safe.
 //
 // Every mbarrier wait is bounded (~2 s): on expiry the context's device error word is set and
-// the CTA drains and returns.  The only hardware barrier is the one among the four prep warps,
+// the CTA drains and returns.  The only hardware barrier is the one among the prep warps,
 // each of which executes it the same fixed number of times per layer.
 #include <stdlib.h>
 
@@ -63,9 +64,17 @@ __device__ __forceinline__ float pow2f(int p) {  // 2^p for p in [-126, 127]
 
 constexpr int MAX_SLOTS = 8;   // ring slots = math warps
 constexpr int MATH_WARPS = 8;  // warps 0..7: one ring slot each
-constexpr int PREP_WARPS = 8;  // warps 8..15: prepare the next layer's activations
+constexpr int PREP_WARPS = 7;  // warps 8..14: prepare the next layer's activations
 constexpr int PREP_THREADS = PREP_WARPS * 32;
 constexpr int THREADS = (MATH_WARPS + PREP_WARPS + 1) * 32;  // + the producer warp (last)
+
+// Per activation buffer: what a math warp needs when it finishes an output.  Kept in shared memory
+// and read at that point, not carried in registers through the dot-product loop (one more live
+// pointer there costs the kernel a tenth of its speed).
+struct LayerConsts {
+    float unscale[2][2];    // per activation row: dot = integer sum * [0] * [1]
+    const float *residual;  // added to the result (laid out like y), or null
+};
 
 struct RingBars {
     uint64_t full[MAX_SLOTS];    // slot's bytes have landed
@@ -73,11 +82,10 @@ struct RingBars {
     uint64_t xs_full[2];         // activation buffer b is prepared (count: prep warps)
     uint64_t xs_empty[2];        // every math warp is done with activation buffer b (count: math warps)
     int abort_flag;
-    int done_warps;              // math warps that have stored all their results (column shards only)
     int bad_warp[PREP_WARPS];    // per prep warp: its part of x holds Inf/NaN
     float xmax[PREP_WARPS][2];   // per prep warp and activation row: max |x|
     int bad[2];                  // per buffer: the layer's x holds Inf/NaN
-    float unscale[2][2][2];      // per buffer and activation row: dot = integer sum * [0] * [1]
+    LayerConsts lc[2];           // per buffer
     float sumsq[2][PREP_WARPS][2];  // RMSNorm input: per layer parity, prep warp and row, sum of x^2
     float rrms[2][2];            // per buffer and activation row: 1 / sqrt(mean(x^2) + eps)
 };
@@ -142,7 +150,7 @@ __device__ __forceinline__ void store_result(float *p, float val, const PeerSet 
 template <int MT, int RW, bool PEER>
 __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_t *st,
                                               const uint4 *xs, int kpad, int rows, int jl0,
-                                              int row0, const float *unscale, const float *scale_s,
+                                              int row0, const LayerConsts *lc, const float *scale_s,
                                               const float *bias_s, bool staged, int lane,
                                               uint32_t empty_bar, const PeerSet &ps) {
     const int k = L.k;
@@ -176,9 +184,11 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
                 }
         }
     }
-    // the slot's bytes have been consumed: hand it back to the producer
+    // The slot's bytes have been consumed: hand it back to the producer.  Lane 31 arrives, a lane
+    // that never stores results: the arrive is a release, and a release issued by a lane whose
+    // earlier stores went to a peer GPU would wait for their acknowledgement over NVLink.
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty_bar);
+    if (lane == 31) mbar_arrive(empty_bar);
     // warp totals (exact integers), then lane r*MT+m finishes output (r, m)
     double mine = 0.0;
 #pragma unroll
@@ -193,11 +203,12 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
     if (lane < rows * MT) {
         const int r = lane / MT, m = lane % MT;
         const int jl = jl0 + r;
-        const float dot = (float)(mine * (double)unscale[m * 2 + 0] * (double)unscale[m * 2 + 1]);
+        const float dot = (float)(mine * (double)lc->unscale[m][0] * (double)lc->unscale[m][1]);
         const float sc = staged ? scale_s[jl] : __ldg(L.scales + row0 + jl);
         float val = __fmul_rn(dot, sc);
         if (L.bias) val = __fadd_rn(val, staged ? bias_s[jl] : __ldg(L.bias + row0 + jl));
-        if (L.residual) val = __fadd_rn(val, L.residual[(size_t)m * L.ldy + row0 + jl]);
+        const float *residual = lc->residual;
+        if (residual) val = __fadd_rn(val, residual[(size_t)m * L.ldy + row0 + jl]);
         store_result<PEER>(L.y + (size_t)m * L.ldy + row0 + jl, val, ps);
     }
 }
@@ -245,24 +256,91 @@ __device__ __noinline__ void consume_stage_fp32(const StreamLayer &L, const uint
         }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty_bar);
+    if (lane == 31) mbar_arrive(empty_bar);
+}
+
+// Prep-warp passes over a layer's activations.  XF = the layer has an input transform; the plain
+// case is kept free of it (a test per element in these loops showed up as 4 % of a 12-layer launch).
+// Pass 1: max |x'| per row and the Inf/NaN flag.
+template <int MT, bool XF>
+__device__ __forceinline__ void prep_scan(const StreamLayer &L, int ptid, int chunks, uint64_t pol_keep,
+                                          const float (&rr)[MT], float (&mx)[MT], int &bad) {
+    const int k = L.k;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+        mx[m] = 0.0f;
+        for (int c = ptid; c < chunks; c += PREP_THREADS) {
+            const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                float4 t4 = ld_f4_hint(p4 + v, pol_keep);
+                if (XF) {
+                    const size_t col = (size_t)c * 16 + 4 * v;
+                    t4.x = input_value(L, t4.x, m, col + 0, rr[m]);
+                    t4.y = input_value(L, t4.y, m, col + 1, rr[m]);
+                    t4.z = input_value(L, t4.z, m, col + 2, rr[m]);
+                    t4.w = input_value(L, t4.w, m, col + 3, rr[m]);
+                }
+                const float a0 = fabsf(t4.x), a1 = fabsf(t4.y), a2 = fabsf(t4.z), a3 = fabsf(t4.w);
+                bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) |
+                       !(a2 <= 3.402823466e38f) | !(a3 <= 3.402823466e38f);
+                mx[m] = fmaxf(fmaxf(mx[m], fmaxf(a0, a1)), fmaxf(a2, a3));
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], o));
+    }
+}
+// Pass 2, one row: digits of rint(x' * f1 * f2) into the row's three planes (x is re-read; it is in
+// L1 now).
+template <bool XF>
+__device__ __forceinline__ void prep_digits(const StreamLayer &L, int m, int ptid, int chunks, int kpad,
+                                            float f1, float f2, float rr, uint4 *plane) {
+    const int k = L.k;
+    for (int c = ptid; c < kpad; c += PREP_THREADS) {
+        uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0, o2 = o0;
+        if (c < chunks) {
+            const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
+            float xv[16];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const float4 t4 = p4[v];
+                xv[4 * v + 0] = t4.x;
+                xv[4 * v + 1] = t4.y;
+                xv[4 * v + 2] = t4.z;
+                xv[4 * v + 3] = t4.w;
+            }
+            if (XF) {
+#pragma unroll
+                for (int v = 0; v < 16; ++v) xv[v] = input_value(L, xv[v], m, (size_t)c * 16 + v, rr);
+            }
+            chunk_digits(xv, f1, f2, o0, o1, o2);
+        }
+        plane[c] = o0;
+        plane[kpad + c] = o1;
+        plane[2 * kpad + c] = o2;
+    }
 }
 
 // MT activation rows per layer (1..2).  `num_slots` ring slots of `slot_bytes`; `kpad_max` = 16-byte
 // chunks per activation row rounded up to 32 for the widest layer; `sb_rows` = capacity of the
 // per-layer scale/bias staging (0: read them from global memory).
 //
-// Warp roles: warps 0..7 math (warp w owns ring slot w), warps 8..15 prepare the NEXT layer's
+// Warp roles: warps 0..7 math (warp w owns ring slot w), warps 8..14 prepare the NEXT layer's
 // activations (digit planes, staged scales) into the other of `num_bufs` buffers while the math
 // warps work on the current layer, the last warp is the producer.
 //
-// PEER (column shards): every result is also stored into the other ranks' windows, each CTA
-// signals its arrival there once its math warps are done, and CTA 0's producer lane - idle once
-// the last copy is issued - waits until every rank's results for this run have arrived here.
+// PEER (column shards): every result is also stored into the other ranks' windows.  The kernel does
+// not announce its own results - a fence that waits for the NVLink acknowledgements, in every CTA,
+// showed up as 8 us on a 72 us launch; it announces the PREVIOUS run of its rank instead, which is
+// complete by the time this grid's dependency is released, from a lane that has nothing else to
+// do.  Nor does it wait for anybody: a waiting CTA would hold its SM, and the completion of the
+// grid, until the slowest rank is through.  The exchange's wait kernel (shard.cu) announces what is
+// still unannounced and waits for the arrivals, on behalf of whoever consumes the gathered result.
 template <int MT, bool PEER>
-__global__ void __launch_bounds__(THREADS, 1)
-qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int kpad_max,
-                    int sb_rows, int num_bufs, int *err, const PeerSet ps) {
+__device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_slots, int slot_bytes,
+                                            int kpad_max, int sb_rows, int num_bufs, int *err,
+                                            const PeerSet &ps) {
     extern __shared__ __align__(128) uint8_t smem[];
     // layout: ring [num_slots][slot_bytes] | xs [num_bufs][MT][3][kpad_max] uint4 | RingBars |
     //         scale_s[num_bufs][sb_rows] | bias_s[num_bufs][sb_rows]
@@ -288,7 +366,6 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
             mbar_init(smem_u32(&bars->xs_empty[b]), MATH_WARPS);
         }
         bars->abort_flag = 0;
-        bars->done_warps = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -329,7 +406,6 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                     }
                 }
             }
-            if (PEER && ok && blockIdx.x == 0) (void)shard_wait_all(ps, abort_flag, err, 0x17);
         }
         return;
     }
@@ -353,7 +429,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
             // Scales and bias are layer constants: fetch this CTA's rows first.  Unconditional
             // loads from clamped addresses, masked afterwards, so that no predicated register
             // write has to wait for a load that is still in flight.
-            float sc_pre[4], bs_pre[4];  // rows ptid, ptid+256, ... of this CTA (at most 4 per thread)
+            float sc_pre[4], bs_pre[4];  // rows ptid, ptid + PREP_THREADS, ... of this CTA (at most 4 per thread)
             if (staged) {
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
@@ -401,30 +477,10 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
             // pass 1: max |x'| and the Inf/NaN flag per activation row
             float mx[MT];
             int bad = 0;
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                mx[m] = 0.0f;
-                for (int c = ptid; c < chunks; c += PREP_THREADS) {
-                    const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        float4 t4 = ld_f4_hint(p4 + v, pol_keep);
-                        if (xform) {
-                            const size_t col = (size_t)c * 16 + 4 * v;
-                            t4.x = input_value(L, t4.x, m, col + 0, rr[m]);
-                            t4.y = input_value(L, t4.y, m, col + 1, rr[m]);
-                            t4.z = input_value(L, t4.z, m, col + 2, rr[m]);
-                            t4.w = input_value(L, t4.w, m, col + 3, rr[m]);
-                        }
-                        const float a0 = fabsf(t4.x), a1 = fabsf(t4.y), a2 = fabsf(t4.z), a3 = fabsf(t4.w);
-                        bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) |
-                               !(a2 <= 3.402823466e38f) | !(a3 <= 3.402823466e38f);
-                        mx[m] = fmaxf(fmaxf(mx[m], fmaxf(a0, a1)), fmaxf(a2, a3));
-                    }
-                }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], o));
-            }
+            if (xform)
+                prep_scan<MT, true>(L, ptid, chunks, pol_keep, rr, mx, bad);
+            else
+                prep_scan<MT, false>(L, ptid, chunks, pol_keep, rr, mx, bad);
             bad = __any_sync(0xffffffffu, bad);
             // The buffer (digits, scales, flags) may still be read by math warps working on layer
             // li - num_bufs: wait until all of them have released it.
@@ -450,6 +506,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
             for (int w = 0; w < PREP_WARPS; ++w) bad |= bars->bad_warp[w];
             if (ptid == 0) {
                 bars->bad[buf] = bad;
+                bars->lc[buf].residual = L.residual;
 #pragma unroll
                 for (int m = 0; m < MT; ++m) bars->rrms[buf][m] = rr[m];
             }
@@ -464,34 +521,14 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                     const int e1 = e >> 1, e2 = e - e1;                     // 2^e = 2^e1 * 2^e2, both finite
                     const float f1 = pow2f(e1), f2 = pow2f(e2);
                     if (ptid == 0) {
-                        bars->unscale[buf][m][0] = pow2f(-e1);
-                        bars->unscale[buf][m][1] = pow2f(-e2);
+                        bars->lc[buf].unscale[m][0] = pow2f(-e1);
+                        bars->lc[buf].unscale[m][1] = pow2f(-e2);
                     }
                     uint4 *plane = xs + (size_t)m * 3 * kpad;
-                    for (int c = ptid; c < kpad; c += PREP_THREADS) {
-                        uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0, o2 = o0;
-                        if (c < chunks) {
-                            const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
-                            float xv[16];
-#pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                const float4 t4 = p4[v];
-                                xv[4 * v + 0] = t4.x;
-                                xv[4 * v + 1] = t4.y;
-                                xv[4 * v + 2] = t4.z;
-                                xv[4 * v + 3] = t4.w;
-                            }
-                            if (xform) {
-#pragma unroll
-                                for (int v = 0; v < 16; ++v)
-                                    xv[v] = input_value(L, xv[v], m, (size_t)c * 16 + v, rr[m]);
-                            }
-                            chunk_digits(xv, f1, f2, o0, o1, o2);
-                        }
-                        plane[c] = o0;
-                        plane[kpad + c] = o1;
-                        plane[2 * kpad + c] = o2;
-                    }
+                    if (xform)
+                        prep_digits<true>(L, m, ptid, chunks, kpad, f1, f2, rr[m], plane);
+                    else
+                        prep_digits<false>(L, m, ptid, chunks, kpad, f1, f2, rr[m], plane);
                 }
             }
             // publish the buffer to the math warps
@@ -502,6 +539,15 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
     }
 
     // ---------------- math warps ----------------
+    if (PEER && blockIdx.x == 0 && warp == MATH_WARPS - 1 && ps.target > 0x100000000ull) {
+        // A warp that has nothing to do until the first layer's activations are prepared announces
+        // this rank's PREVIOUS run to the other ranks: once the grids before this one have
+        // completed, that run's stores are performed.  (This run is announced by the next one, or
+        // by the exchange's wait kernel.)
+        grid_dependency_wait();
+        if (lane == 0) shard_publish(ps, ps.target - 0x100000000ull);
+        __syncwarp();
+    }
     int g_base = 0;  // global stage index of the current layer's first stage (in this CTA)
     for (int li = 0; li < batch.count; ++li) {
         const StreamLayer L = layers[li];
@@ -519,7 +565,7 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
         (void)mbar_wait(smem_u32(&bars->xs_full[buf]), (uint32_t)(li / num_bufs) & 1u, abort_flag, err,
                         0x16);
         const int bad = bars->bad[buf];
-        const float *unscale = &bars->unscale[buf][0][0];
+        const LayerConsts *lc = &bars->lc[buf];
 
         // Warp w takes the global stages g with g % num_slots == w.  One slot, one warp: a warp
         // never waits on a barrier that is more than one phase behind it, which is what the
@@ -538,13 +584,13 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
                     consume_stage_fp32<MT, PEER>(L, st, L.rw, rows, s * L.rw, row0, lane, empty_bar, ps,
                                                  &bars->rrms[buf][0]);
                 } else if (L.rw == 4) {
-                    consume_stage<MT, 4, PEER>(L, st, xs, kpad, rows, s * 4, row0, unscale, scale_s, bias_s,
+                    consume_stage<MT, 4, PEER>(L, st, xs, kpad, rows, s * 4, row0, lc, scale_s, bias_s,
                                                staged, lane, empty_bar, ps);
                 } else if (L.rw == 2) {
-                    consume_stage<MT, 2, PEER>(L, st, xs, kpad, rows, s * 2, row0, unscale, scale_s, bias_s,
+                    consume_stage<MT, 2, PEER>(L, st, xs, kpad, rows, s * 2, row0, lc, scale_s, bias_s,
                                                staged, lane, empty_bar, ps);
                 } else {
-                    consume_stage<MT, 1, PEER>(L, st, xs, kpad, rows, s, row0, unscale, scale_s, bias_s,
+                    consume_stage<MT, 1, PEER>(L, st, xs, kpad, rows, s, row0, lc, scale_s, bias_s,
                                                staged, lane, empty_bar, ps);
                 }
             }
@@ -552,24 +598,34 @@ qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int 
         g_base += nst;
         // this warp is done with the layer's activation buffer
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bars->xs_empty[buf]));
+        if (lane == 31) mbar_arrive(smem_u32(&bars->xs_empty[buf]));
     }
-    if (PEER) {
-        // The warp's stores to the windows are fenced to system scope before it is counted; the
-        // warp that completes the count fences again (it now stands for all eight) and signals.
-        __syncwarp();
-        if (lane == 0) {
-            __threadfence_system();
-            if (atomicAdd(&bars->done_warps, 1) == MATH_WARPS - 1)
-                shard_signal(ps, (int)blockIdx.x, (int)gridDim.x);
-        }
-    }
+}
+
+// The two entry points.  Sixteen warps of 128 registers fill an SM's register file; the column-shard
+// variant is held to 120 so that a one-warp kernel of the exchange (the arrival wait, on a second
+// stream) finds room beside a resident CTA instead of waiting for the grid to end.
+template <int MT>
+__global__ void __launch_bounds__(THREADS, 1)
+qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int kpad_max, int sb_rows,
+                    int num_bufs, int *err) {
+    const PeerSet none;
+    stream_body<MT, false>(batch, num_slots, slot_bytes, kpad_max, sb_rows, num_bufs, err, none);
+}
+template <int MT>
+__global__ void __maxnreg__(120)
+qgemv_stream_peer_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int kpad_max, int sb_rows,
+                         int num_bufs, int *err, const PeerSet ps) {
+    stream_body<MT, true>(batch, num_slots, slot_bytes, kpad_max, sb_rows, num_bufs, err, ps);
 }
 
 template <int MT, bool PEER>
 int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot_bytes, int kpad,
                      int sb_rows, int bufs, size_t smem, int grid, const PeerSet &ps, cudaStream_t s) {
-    NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_kernel<MT, PEER>, smem));
+    if (PEER)
+        NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_peer_kernel<MT>, smem));
+    else
+        NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_kernel<MT>, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3((unsigned)THREADS);
@@ -580,8 +636,10 @@ int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, qgemv_stream_kernel<MT, PEER>, batch, slots, slot_bytes, kpad,
-                                       sb_rows, bufs, ctx->err_word, ps);
+    cudaError_t e = PEER ? cudaLaunchKernelEx(&cfg, qgemv_stream_peer_kernel<MT>, batch, slots, slot_bytes,
+                                              kpad, sb_rows, bufs, ctx->err_word, ps)
+                         : cudaLaunchKernelEx(&cfg, qgemv_stream_kernel<MT>, batch, slots, slot_bytes, kpad,
+                                              sb_rows, bufs, ctx->err_word);
     count_launch();
     if (e != cudaSuccess)
         return fail(NNE_ERR_CUDA, "streaming kernel launch failed: %s", cudaGetErrorString(e));

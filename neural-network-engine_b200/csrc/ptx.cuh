@@ -48,7 +48,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false if the wait ran out (or another role already gave up); the
 // caller then leaves its loops.  `abort_flag` is a CTA-shared word, `err` the context's.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
-                                          int *err, int where) {
+                                          int *err, int where,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
@@ -56,7 +57,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++spins & 0x3ff) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 // The context's error word lives in mapped host memory (the host reads it after a
                 // synchronise without a copy): a plain store, the last writer wins.

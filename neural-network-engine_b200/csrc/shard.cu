@@ -10,18 +10,20 @@
 //    shapes the streaming GEMV does that itself - its finishing lanes store each result to every
 //    window (gemv_tma.cu) - and for every other shape shard_push_kernel below copies the slice
 //    out after the local forward.  Plain st.global to peer-mapped memory only: no multicast
-//    object, no TMA to or from a peer.  Arrival is counted per source rank in 64-bit words in
-//    each window: CTA 0 of a source adds 2^32 - (grid - 1), every other CTA adds 1, so a word
-//    reaches epoch * 2^32 exactly when every CTA of that source's run number `epoch` has stored
-//    and fenced, whatever its grid size.  CTA 0 of the same kernel then waits (bounded, about 2 s)
-//    until all sources have arrived, so "my kernel finished" means "my window holds every slice".
+//    object, no TMA to or from a peer.  A run is split in two, like a non-blocking collective:
+//    the producing kernels only store (they neither announce nor wait); nne_shard_group_wait then
+//    enqueues a one-warp kernel that announces this rank's completed runs in every window (one
+//    64-bit word per source rank) and waits, bounded at about 2 s, until every rank has announced
+//    as much - at which point this rank's window holds every slice.  Every rank must call it.
 //  * NCCL (north star's baseline): ncclAllGather on a communicator the host created.  The library
 //    resolves the NCCL entry points at run time from the copy the process has already loaded.
 //
-// Ordering rule for callers (both routes): all ranks issue the same sequence of sharded runs on
-// a group, like collectives, and a window location must not be the target of two consecutive
-// runs (alternate two output areas): a rank may start run e+1 while a peer still reads run e's
-// result.
+// Ordering rules for callers: all ranks issue the same sequence of sharded runs and waits on a
+// group, like collectives; a wait goes on a stream that is ordered after the runs it completes.  A
+// rank may overwrite an output area only when every peer has finished READING what the area held.
+// With run, wait and the reads in one stream, "a peer has announced run e+1" implies "it has read
+// run e", so two areas that alternate are enough; a caller that keeps d runs in flight before it
+// waits needs 2 d areas.
 #include <dlfcn.h>
 #include <string.h>
 
@@ -38,11 +40,9 @@ namespace {
 
 // ---- push kernel ----------------------------------------------------------------------------
 // Copies this rank's slices (rows x width floats at row stride ldy) from its own window to the
-// same place in every other window, then signals and waits as described above.
+// same place in every other window.
 __global__ void __launch_bounds__(256)
-shard_push_kernel(const PushSeg *__restrict__ segs, int count, const PeerSet ps, int *err) {
-    __shared__ int abort_flag;
-    if (threadIdx.x == 0) abort_flag = 0;
+shard_push_kernel(const PushSeg *__restrict__ segs, int count, const PeerSet ps) {
     // the slices are the output of the previous kernels in the stream
     grid_dependency_wait();
     grid_launch_dependents();
@@ -76,10 +76,23 @@ shard_push_kernel(const PushSeg *__restrict__ segs, int count, const PeerSet ps,
             }
         }
     }
-    __syncthreads();
+}
+
+// The second half of the exchange, one warp: announces this rank's runs up to ps.target to every
+// rank - the producing kernels precede this kernel in stream order, so their stores, local and
+// remote, are complete - and then waits (bounded) until every rank has announced as much, i.e.
+// until this rank's window holds every slice of those runs.  Small enough to sit on an SM beside a
+// CTA of the persistent decode kernel, so on a second stream it overlaps the next run.
+// (Announcing from inside the producing kernels was measured and dropped: a fence that waits for
+// the NVLink acknowledgements in every CTA cost 8 us on a 72 us launch, and an announcing kernel
+// between two forwards in one stream as much.)
+__global__ void __launch_bounds__(32)
+shard_wait_kernel(const PeerSet ps, int *err) {
+    __shared__ int abort_flag;
     if (threadIdx.x == 0) {
-        shard_signal(ps, (int)blockIdx.x, (int)gridDim.x);
-        if (blockIdx.x == 0) shard_wait_all(ps, &abort_flag, err, 0x51);
+        abort_flag = 0;
+        shard_publish(ps, ps.target);
+        (void)shard_wait_all(ps, &abort_flag, err, 0x51);
     }
 }
 
@@ -94,6 +107,33 @@ shard_interleave_kernel(const float *__restrict__ staged, float *__restrict__ y,
         const size_t g = i / (m * w), rem = i - g * (m * w);
         const size_t r = rem / w, c = rem - r * w;
         y[r * ldy + g * w + c] = staged[i];
+    }
+}
+
+// Failure-path check, no fault involved: one CTA waits on something that will never happen - an
+// mbarrier nobody arrives at (which = 0), or an arrival word that nothing raises (which = 1) - with
+// a short limit.  The wait must give up, set the context's error word and let the kernel return.
+__global__ void __launch_bounds__(32)
+wait_selftest_kernel(int which, unsigned long long limit_ns, unsigned long long *never_raised, int *err) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        if (which == 0) {
+            (void)mbar_wait(smem_u32(&bar), 0, &abort_flag, err, 0x7e, limit_ns);
+        } else {
+            PeerSet ps;
+            ps.world = 1;
+            ps.rank = 0;
+            ps.target = ~0ull;
+            ps.flags = never_raised;
+            (void)shard_wait_all(ps, &abort_flag, err, 0x7f, limit_ns);
+        }
     }
 }
 
@@ -163,9 +203,17 @@ int shard_push(nne_shard_group *g, const PushSeg *segs_dev, int count, size_t fl
     cfg.stream = s;
     cfg.attrs = pdl;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, shard_push_kernel, segs_dev, count, ps, g->ctx->err_word);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, shard_push_kernel, segs_dev, count, ps);
     count_launch();
     if (e != cudaSuccess) return fail(NNE_ERR_CUDA, "slice push launch failed: %s", cudaGetErrorString(e));
+    return NNE_OK;
+}
+
+int shard_wait(nne_shard_group *g, unsigned long long epoch, cudaStream_t s) {
+    if (g->world <= 1 || epoch == 0) return NNE_OK;
+    const PeerSet ps = shard_peerset(g, epoch);
+    shard_wait_kernel<<<1, 32, 0, s>>>(ps, g->ctx->err_word);
+    NNE_LAUNCH_CHECK();
     return NNE_OK;
 }
 
@@ -207,6 +255,23 @@ int shard_interleave(nne_ctx *ctx, const float *staged, float *y, int world, siz
 using namespace nne;
 
 extern "C" {
+
+int nne_cuda_ctx_selftest_wait(nne_ctx *ctx, int which, unsigned int limit_us) {
+    NNE_GUARD_BEGIN
+    NNE_TRY(use_ctx(ctx));
+    if (which != 0 && which != 1) return fail(NNE_ERR_INVALID_ARGUMENT, "which must be 0 or 1");
+    if (limit_us == 0 || limit_us > 1000000u)
+        return fail(NNE_ERR_INVALID_ARGUMENT, "limit must be 1..1000000 microseconds");
+    // the context's 256-byte scratch block is zero beyond its first word: bytes 8..15 serve as the
+    // arrival word that never reaches its target
+    wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(which, (unsigned long long)limit_us * 1000ull,
+                                                   reinterpret_cast<unsigned long long *>(ctx->absmax_word + 2),
+                                                   ctx->err_word);
+    NNE_LAUNCH_CHECK();
+    NNE_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    return NNE_OK;
+    NNE_GUARD_END
+}
 
 int nne_shard_group_create(nne_ctx *ctx, int rank, int world, size_t window_bytes,
                            nne_shard_group **out) {
@@ -312,6 +377,14 @@ int nne_shard_group_window(const nne_shard_group *g, void **base, size_t *bytes)
     if (base) *base = g->base;
     if (bytes) *bytes = g->flag_off;
     return NNE_OK;
+}
+
+int nne_shard_group_wait(nne_shard_group *g, void *stream) {
+    NNE_GUARD_BEGIN
+    if (!g) return fail(NNE_ERR_INVALID_ARGUMENT, "null group");
+    NNE_TRY(use_ctx(g->ctx));
+    return shard_wait(g, g->epoch.load(), (cudaStream_t)stream);
+    NNE_GUARD_END
 }
 
 int nne_shard_group_set_nccl(nne_shard_group *g, void *nccl_comm) {

@@ -33,19 +33,18 @@ struct PushSeg {
 };
 
 #ifdef __CUDACC__
-// Called by ONE thread of CTA `cta` of `grid` after the CTA's stores to the windows are complete
-// (and ordered before this thread by a CTA or warp barrier): fences them to system scope and adds
-// this CTA's share to the arrival word "from ps.rank" in every window.  The shares of a whole grid
-// add up to 2^32 whatever the grid size: CTA 0 contributes 2^32 - (grid - 1), the others 1.
-__device__ __forceinline__ void shard_signal(const PeerSet &ps, int cta, int grid) {
-    __threadfence_system();
-    const unsigned long long share = (cta == 0) ? (0x100000000ull - (unsigned long long)(grid - 1)) : 1ull;
+// Announces this rank's runs up to number `upto` (epoch * 2^32) to every rank: raises the word
+// "from ps.rank" in every window.  Called by one thread of a kernel that runs AFTER the producing kernels have
+// completed (stream order), so their stores - local and remote - are already performed; the fence
+// makes the announcement a release that carries them.
+__device__ __forceinline__ void shard_publish(const PeerSet &ps, unsigned long long upto) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
 #pragma unroll
     for (int p = 0; p < SHARD_MAX_RANKS; ++p) {
         if (p < ps.world) {
             unsigned long long *word = reinterpret_cast<unsigned long long *>(
                                            reinterpret_cast<char *>(ps.flags) + ps.delta[p]) + ps.rank;
-            asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(word), "l"(share) : "memory");
+            asm volatile("red.relaxed.sys.global.max.u64 [%0], %1;" ::"l"(word), "l"(upto) : "memory");
         }
     }
 }
@@ -53,7 +52,7 @@ __device__ __forceinline__ void shard_signal(const PeerSet &ps, int cta, int gri
 // Waits until every source's arrival word in THIS rank's window has reached the run's target.
 // Bounded like every wait in this library; on expiry sets the context's error word and returns false.
 __device__ __forceinline__ bool shard_wait_all(const PeerSet &ps, volatile int *abort_flag, int *err,
-                                               int where) {
+                                               int where, unsigned long long limit_ns = WAIT_LIMIT_NS) {
     const unsigned long long t0 = globaltimer_ns();
     for (int s = 0; s < ps.world; ++s) {
         unsigned int spins = 0;
@@ -63,7 +62,7 @@ __device__ __forceinline__ bool shard_wait_all(const PeerSet &ps, volatile int *
             if (v >= ps.target) break;
             if ((++spins & 0xff) == 0) {
                 if (*abort_flag) return false;
-                if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                if (globaltimer_ns() - t0 > limit_ns) {
                     *abort_flag = 1;
                     *reinterpret_cast<volatile int *>(err) = 0x100 + where;
                     __threadfence_system();
@@ -95,6 +94,7 @@ namespace nne {
 PeerSet shard_peerset(const nne_shard_group *g, unsigned long long epoch);
 int shard_push(nne_shard_group *g, const PushSeg *segs_dev, int count, size_t floats_total,
                unsigned long long epoch, cudaStream_t s);
+int shard_wait(nne_shard_group *g, unsigned long long epoch, cudaStream_t s);
 int shard_nccl_all_gather(nne_shard_group *g, const void *send, void *recv, size_t count_floats,
                           cudaStream_t s);
 int shard_nccl_group_start();

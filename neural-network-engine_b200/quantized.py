@@ -379,6 +379,100 @@ class QLinearPlan:
             pass
 
 
+# ---- device-resident tensors: GpuTensor / ToGpu / GpuLinear of the device backend -----------------
+class CudaTensor:
+    """f32 tensor in device memory; the `GpuTensor` of this backend (src/gpu/tensor.rs:12-16):
+    `from_slice` / `from_raw` upload (:19-50), `to_cpu` downloads (:53-95), `shape` (:98-100)."""
+
+    def __init__(self, ptr: int, shape, ctx: CudaContext, owner: bool = True):
+        self.ptr, self.shape, self.ctx, self._owner = int(ptr), [int(s) for s in shape], ctx, owner
+
+    @classmethod
+    def empty(cls, shape, ctx: Optional[CudaContext] = None) -> "CudaTensor":
+        ctx = ctx or default_context()
+        n = int(np.prod(shape, dtype=np.int64)) if len(shape) else 1
+        p = C.c_void_p()
+        try:
+            check(load().nne_device_alloc(ctx.handle, 4 * n, C.byref(p)))
+        except NneError as e:
+            _raise_mapped(e)
+        return cls(p.value, shape, ctx)
+
+    @classmethod
+    def from_raw(cls, raw: np.ndarray, ctx: Optional[CudaContext] = None) -> "CudaTensor":
+        a = np.ascontiguousarray(raw, dtype=np.float32)  # to_contiguous(), src/gpu/tensor.rs:48
+        t = cls.empty(a.shape, ctx)
+        try:
+            check(load().nne_device_upload(t.ctx.handle, t.ptr, _ptr(a), a.nbytes))
+        except NneError as e:
+            _raise_mapped(e)
+        return t
+
+    @classmethod
+    def from_slice(cls, values, shape, ctx: Optional[CudaContext] = None) -> "CudaTensor":
+        a = np.asarray(values, dtype=np.float32).reshape(-1)
+        if a.size != int(np.prod(shape, dtype=np.int64)):  # IncompatibleShapes, src/gpu/tensor.rs:21-26
+            raise InvalidArgument(f"GpuTensor::from_slice: {a.size} values for shape {list(shape)}")
+        return cls.from_raw(a.reshape(shape), ctx)
+
+    def numel(self) -> int:
+        return int(np.prod(self.shape, dtype=np.int64)) if self.shape else 1
+
+    def to_cpu(self) -> np.ndarray:
+        out = np.empty(self.shape, dtype=np.float32)
+        try:
+            check(load().nne_device_download(self.ctx.handle, _ptr(out), self.ptr, out.nbytes))
+        except NneError as e:
+            _raise_mapped(e)
+        return out
+
+    def close(self):
+        if self._owner and self.ptr:
+            load().nne_device_free(self.ctx.handle, self.ptr)
+        self.ptr = 0
+
+    def __del__(self):  # pragma: no cover - best effort
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class CudaQLinear:
+    """`QLinear` placed on the device: the `GpuLinear` of this backend (src/gpu/layers.rs:24-43).
+    `forward` takes and returns device tensors and is asynchronous on the context's stream; nothing
+    crosses PCIe until `to_cpu`."""
+
+    def __init__(self, layer: "QLinear", ctx: CudaContext):
+        self.layer, self.ctx = layer, ctx
+        self.in_features, self.out_features = layer.in_features, layer.out_features
+
+    def forward(self, input: CudaTensor) -> CudaTensor:
+        if len(input.shape) < 2:
+            raise InvalidArgument(
+                f"QLinear forward expects tensor with at least 2 dimensions, got {input.shape}")
+        if input.shape[-1] != self.in_features:
+            raise ShapeMismatch([self.in_features], [input.shape[-1]])
+        m = int(np.prod(input.shape[:-1], dtype=np.int64))
+        out = CudaTensor.empty(input.shape[:-1] + [self.out_features], self.ctx)
+        self.layer.forward_device(input.ptr, m, out.ptr, load().nne_cuda_ctx_stream(self.ctx.handle) or 0)
+        return out
+
+
+def _qlinear_to_gpu(self, ctx: Optional[CudaContext] = None) -> CudaQLinear:
+    """`impl ToGpu for QLinear` (the trait of src/gpu/layers.rs:12-15): the layer's device-resident
+    form.  Its weights already live on the device, so nothing is uploaded again when the context is
+    the layer's own; another context gets its own copy of the codes."""
+    ctx = ctx or self._ctx or default_context()
+    if self._ctx is not None and ctx is not self._ctx:
+        return CudaQLinear(QLinear.from_fields(self.qweight, self.scales, self.bias, self.in_features,
+                                               self.out_features, ctx), ctx)
+    return CudaQLinear(self, ctx)
+
+
+QLinear.to_gpu = _qlinear_to_gpu
+
+
 # ---- the steps either side of a QLinear in a decoder block ---------------------------------------
 def rmsnorm_device(ctx: CudaContext, x_ptr: int, gamma_ptr: int, eps: float, rows: int, cols: int,
                    y_ptr: int, stream: int = 0) -> None:

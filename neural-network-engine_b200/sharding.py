@@ -140,6 +140,10 @@ class ShardGroup:
         self._nccl = comm or NcclComm(self.rank, self.world, f"cuda:{self.ctx.device}")
         check(load().nne_shard_group_set_nccl(self._h, self._nccl.comm))
 
+    def wait(self, stream: int = 0) -> None:
+        """Enqueues the wait for the arrival of every sharded run issued so far (peer-store route)."""
+        check(load().nne_shard_group_wait(self._h, stream))
+
     def alloc(self, nfloats: int) -> int:
         """Device pointer to `nfloats` f32 of window space (256-byte aligned)."""
         off = (self._top + 255) & ~255
@@ -239,6 +243,8 @@ class ShardedQLinear:
         self._turn += 1
         plan = self._plan(x_dev.data_ptr(), m, area)
         plan.run(stream)
+        if self.route == ROUTE_PEER_STORES:
+            self.group.wait(stream)  # the reader of the result follows on this stream
         return torch.as_tensor(DeviceArray(self._areas[area], (m, self.out_features)),
                                device=f"cuda:{self.group.ctx.device}")
 

@@ -81,6 +81,45 @@ def test_c_oracle_matches_numpy_restatement():
     assert int(q.min()) >= -127 and int(q.max()) == 127  # -128 is unreachable on finite rows
 
 
+def test_forward_oracle_matches_the_second_restatement_of_the_avx2_dot(golden):
+    """The forward has two restatements written from the Rust lines independently: the C oracle
+    (AVX2 intrinsics, as the reference) and numpy with an emulated fused multiply-add.  They must
+    agree BIT FOR BIT on the golden case, on lengths that end in a scalar tail, and on inputs with a
+    wide dynamic range (where a double-rounded FMA emulation would show)."""
+    if not oracle.lib().nne_ref_has_avx2_fma():
+        pytest.skip("host without AVX2/FMA: the C oracle cannot run the reference's SIMD branch")
+    n = int(golden["n_forward"])
+    q, s, b, x = golden["q"][:n], golden["scales"][:n], golden["bias"][:n], golden["x"]
+    y_np = oracle.numpy_forward_avx2(q, s, b, x)
+    assert np.array_equal(y_np.view(np.uint32), golden["y_avx2"].view(np.uint32))
+    assert np.array_equal(oracle.numpy_forward_avx2(q, s, None, x).view(np.uint32),
+                          golden["y_nobias"].view(np.uint32))
+    rng = np.random.default_rng(11)
+    for k in (1, 15, 16, 17, 31, 250, 1003):
+        w = oracle.normal(70, k, (6, k), 0.0, 0.02)
+        qq, ss = oracle.quantize_rows(w)
+        xx = (rng.standard_normal((2, k)) * np.exp2(rng.integers(-18, 18, (2, k)))).astype(np.float32)
+        a = oracle.forward(qq, ss, None, xx, threads=1, use_avx2=1)
+        assert np.array_equal(a.view(np.uint32), oracle.numpy_forward_avx2(qq, ss, None, xx).view(np.uint32)), k
+
+
+def test_rms_norm_and_silu_mul_restatements():
+    """RMSNorm (src/nn/norm.rs:517-577, both branches) and silu(gate) * up against float64 numpy."""
+    x = oracle.normal(71, 0, (5, 1003), 0.0, 2.0)
+    g = oracle.normal(71, 1, (1003,), 1.0, 0.2)
+    ref = x.astype(np.float64) / np.sqrt((x.astype(np.float64) ** 2).mean(-1, keepdims=True) + 1e-6) * g
+    for avx in (0, 1):
+        if avx and not oracle.lib().nne_ref_has_avx2_fma():
+            continue
+        assert np.abs(oracle.rms_norm(x, g, 1e-6, avx) - ref).max() <= 1e-5 * np.abs(ref).max()
+    ones = oracle.rms_norm(np.full((1, 8), 3.0, np.float32), np.ones(8, np.float32), 0.0, 0)
+    assert np.array_equal(ones, np.ones((1, 8), np.float32))          # 3 / sqrt(9) = 1 exactly
+    gate = np.array([0.0, 1.0, -1.0, 30.0, -30.0], np.float32)
+    up = np.array([2.0, 2.0, 2.0, 0.5, 4.0], np.float32)
+    want = gate.astype(np.float64) / (1 + np.exp(-gate.astype(np.float64))) * up
+    assert np.abs(oracle.silu_mul(gate, up) - want).max() <= 1e-6
+
+
 def test_generator_is_deterministic_and_normal():
     a = oracle.normal(3, 5, (1 << 16,))
     b = oracle.normal(3, 5, (1 << 16,))

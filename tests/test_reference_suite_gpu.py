@@ -103,3 +103,32 @@ def test_qlinear_saved_as_int8_loads_straight_onto_the_device(nne, ctx, tmp_path
         assert np.array_equal(back.forward(x).view(np.uint32), ql.forward(x).view(np.uint32))
         assert np.array_equal(back_nb.forward(x).view(np.uint32), nb.forward(x).view(np.uint32))
     ctx.check()
+
+
+def test_device_tensor_chain_stays_on_the_device(nne, ctx):
+    """`ToGpu for QLinear` + `CudaTensor` (the GpuLinear / GpuTensor pattern of the reference's device
+    backend, src/gpu/layers.rs:12-57, src/gpu/tensor.rs:12-100): three layers chained on device
+    tensors give what three host forwards give, bit for bit, with one upload and one download."""
+    dims = [(256, 192), (320, 256), (128, 320)]
+    layers = [nne.QLinear.from_linear(new_linear(nne, 70 + i, k, n), ctx) for i, (n, k) in enumerate(dims)]
+    gpu_layers = [l.to_gpu(ctx) for l in layers]
+    for shape in ([1, 192], [5, 192], [2, 3, 192], [40, 192]):
+        x = oracle.normal(71, len(shape) * shape[0], shape)
+        t = nne.CudaTensor.from_raw(x, ctx)
+        assert t.shape == shape
+        for gl in gpu_layers:
+            t = gl.forward(t)
+        want = x
+        for l in layers:
+            want = l.forward(want)
+        got = t.to_cpu()
+        assert got.shape == want.shape and np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    with pytest.raises(nne.ShapeMismatch):
+        gpu_layers[0].forward(nne.CudaTensor.from_raw(np.zeros((2, 100), np.float32), ctx))
+    with pytest.raises(nne.InvalidArgument):
+        gpu_layers[0].forward(nne.CudaTensor.from_raw(np.zeros((192,), np.float32), ctx))
+    with pytest.raises(nne.InvalidArgument):
+        nne.CudaTensor.from_slice([1.0, 2.0, 3.0], [2, 2], ctx)
+    assert np.array_equal(nne.CudaTensor.from_slice([1.0, 2.0, 3.0, 4.0], [2, 2], ctx).to_cpu(),
+                          np.array([[1, 2], [3, 4]], np.float32))
+    ctx.check()
