@@ -4,14 +4,18 @@
 //! `Arc`-shared context, device failures reported as `EngineError::GpuError(String)`.  There is
 //! no CPU fallback: if the library cannot reach an sm_100 device every call returns `GpuError`.
 pub mod ffi;
+pub mod layers;
 pub mod qlinear;
+pub mod tensor;
 
 use crate::error::{EngineError, Result};
 use std::ffi::CStr;
 use std::os::raw::{c_char, c_int};
 use std::sync::{Arc, OnceLock};
 
+pub use layers::{CudaPlan, CudaQLinearLayer, PlanItem, ToCuda};
 pub use qlinear::CudaQLinear;
+pub use tensor::CudaTensor;
 
 /// Text of the calling thread's last library error.
 fn last_error() -> String {

@@ -30,6 +30,10 @@ impl CudaQLinear {
         Ok(Self { raw, _ctx: ctx.clone() })
     }
 
+    pub(crate) fn raw(&self) -> *mut ffi::nne_qlinear {
+        self.raw
+    }
+
     /// Copy codes and scales back into the host fields of `QLinear`.
     pub fn download(&self, q: &mut [i8], scales: &mut [f32]) -> Result<()> {
         check(unsafe { ffi::nne_qlinear_download(self.raw, q.as_mut_ptr(), scales.as_mut_ptr()) })

@@ -102,6 +102,14 @@ impl QLinear {
         Self { qweight, scales, bias, in_features, out_features, device: slot }
     }
 
+    /// Builds a layer from its public fields (a loaded or hand-made set of codes); the device copy
+    /// is created from them on first use.  Equivalent to a struct literal in the CPU version.
+    pub fn from_parts(qweight: Vec<i8>, scales: Vec<f32>, bias: Option<Vec<f32>>, in_features: usize, out_features: usize) -> Self {
+        assert_eq!(qweight.len(), out_features * in_features, "qweight length must match out_features * in_features");
+        assert_eq!(scales.len(), out_features, "one scale per output channel");
+        Self { qweight, scales, bias, in_features, out_features, device: DeviceSlot::default() }
+    }
+
     fn device(&self) -> Result<&Arc<CudaQLinear>> {
         self.device
             .0

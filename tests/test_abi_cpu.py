@@ -78,3 +78,27 @@ def test_host_side_validation_needs_no_device(nne):
         ql.forward(np.zeros((4, 5), np.float32))
     assert e.value.expected == [2] and e.value.actual == [5]
     assert ql.memory_bytes() == 6 + 12 and ql.parameters() == []
+
+
+def test_rust_bindings_match_the_header():
+    """rust/src/gpu/cuda/ffi.rs is generated from include/nne_cuda.h; a header change without a
+    regenerated ffi.rs (or a hand edit of ffi.rs) fails here.  Also: one declaration per symbol."""
+    import importlib.util
+    gen_path = os.path.join(ROOT, "neural-network-engine_b200", "rust", "gen_ffi.py")
+    spec = importlib.util.spec_from_file_location("gen_ffi", gen_path)
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    want = gen.generate(open(HEADER).read())
+    have = open(gen.OUT).read()
+    assert have == want, "ffi.rs is out of date: run neural-network-engine_b200/rust/gen_ffi.py"
+    rust_syms = sorted(re.findall(r"pub fn (nne_\w+)\(", have))
+    assert rust_syms == declared_symbols()
+
+
+def test_rust_build_script_takes_every_kernel_file():
+    """build.rs scans cuda/ instead of listing files, and every .cu of csrc/ is a kernel file the
+    Makefile builds too (so the two build recipes cannot disagree about the file set)."""
+    text = open(os.path.join(ROOT, "neural-network-engine_b200", "rust", "build.rs")).read()
+    assert "read_dir(\"cuda\")" in text and ".cu\"" not in text.replace('x == "cu"', "")
+    mk = open(os.path.join(ROOT, "neural-network-engine_b200", "csrc", "Makefile")).read()
+    assert "$(wildcard *.cu)" in mk
