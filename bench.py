@@ -348,7 +348,7 @@ def run_native(args):
         return step
 
     step = stepper(plans, wait=(world > 1 and head_route == 0))
-    R = REPEATS_PER_STEP
+    R = max(1, args.repeats)
     for _ in range(max(args.warmup, 3)):
         step()
     step.drain()
@@ -555,14 +555,23 @@ def run_native(args):
     h2d = sum(4 * L["k"] for L in layers)
     d2h = 4 * world * y_total
 
-    sweep = prefill = stack = quant = None
+    sweep = prefill = stack = quant = config5 = None
+    want = set(args.sections.split(","))
+
+    def on(name):
+        return "all" in want or name in want
     if world == 1:
-        sweep = run_decode_sweep(nne, lib, ctx, dev, layers, args)          # config 2, M in 1..16
-        prefill = run_prefill(nne, lib, ctx, dev, make_layer, peaks, args)  # config 3
-        stack = run_stack(nne, lib, ctx, dev, make_layer, peaks, args)      # config 4
-        quant = run_quantize(nne, lib, ctx, dev, peaks, args)               # QLinear::from_linear
-    config5 = run_config5(nne, lib, ctx, dev, group, rank, world, make_layer, peaks, args,
-                          barrier, max_over_ranks)
+        if on("sweep"):
+            sweep = run_decode_sweep(nne, lib, ctx, dev, layers, args)          # config 2, M in 1..16
+        if on("prefill"):
+            prefill = run_prefill(nne, lib, ctx, dev, make_layer, peaks, args)  # config 3
+        if on("stack"):
+            stack = run_stack(nne, lib, ctx, dev, make_layer, peaks, args)      # config 4
+        if on("quantize"):
+            quant = run_quantize(nne, lib, ctx, dev, peaks, args)               # QLinear::from_linear
+    if on("config5"):
+        config5 = run_config5(nne, lib, ctx, dev, group, rank, world, make_layer, peaks, args,
+                              barrier, max_over_ranks)
 
     out = None
     if rank == 0:
@@ -964,6 +973,11 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--repeats", type=int, default=REPEATS_PER_STEP,
+                    help="plan launches per reported step (1 for a short run under a profiler)")
+    ap.add_argument("--sections", default="all",
+                    help="comma list of the extra sections to run besides the headline workload: "
+                         "sweep,prefill,stack,quantize,config5 (a short list keeps a profiler capture small)")
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     args = ap.parse_args()
     if args.impl == "reference":

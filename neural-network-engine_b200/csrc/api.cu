@@ -682,9 +682,9 @@ int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, siz
     nne_ctx *ctx = ql->ctx;
     NNE_TRY(use_ctx(ctx));
     std::lock_guard<std::mutex> lock(ctx->mu);
+    cudaStream_t s = ctx->stream;
     NNE_TRY(ctx->stage_a.reserve(xb ? xb : 4));
     NNE_TRY(ctx->stage_b.reserve(yb));
-    cudaStream_t s = ctx->stream;
     if (xb) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, x_host, xb, cudaMemcpyHostToDevice, s));
     NNE_TRY(forward_dev(ql, (const float *)ctx->stage_a.ptr, m, k, (float *)ctx->stage_b.ptr, ql->n, s));
     NNE_CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_b.ptr, yb, cudaMemcpyDeviceToHost, s));

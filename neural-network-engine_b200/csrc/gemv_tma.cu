@@ -117,7 +117,7 @@ __device__ __forceinline__ void chunk_digits(const float (&xv)[16], float f1, fl
         d[0][w] = d[1][w] = d[2][w] = 0u;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const int v = __float2int_rn(xv[4 * w + b] * f1 * f2);
+            const int v = rint_small(xv[4 * w + b] * f1 * f2);  // |v| <= 2^20
             const int d0 = ((v + 64) & 127) - 64;
             const int v1 = (v - d0) >> 7;
             const int d1 = ((v1 + 64) & 127) - 64;

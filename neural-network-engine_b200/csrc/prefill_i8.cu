@@ -405,7 +405,7 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
             uint32_t w0 = 0u, w1 = 0u;
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const int v = bad ? 0 : __float2int_rn(xv[b] * f1 * f2);
+                const int v = bad ? 0 : rint_small(xv[b] * f1 * f2);  // |v| <= 2^13
                 const int d0 = ((v + 64) & 127) - 64;
                 const int d1 = (v - d0) >> 7;
                 w0 |= (uint32_t)(d0 & 0xff) << (8 * b);
@@ -503,7 +503,7 @@ x_to_digits_bulk_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, in
             uint32_t w0 = 0u, w1 = 0u;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int v = bad ? 0 : __float2int_rn(xv[c] * f1 * f2);
+                const int v = bad ? 0 : rint_small(xv[c] * f1 * f2);  // |v| <= 2^13
                 const int d0 = ((v + 64) & 127) - 64;
                 const int d1 = (v - d0) >> 7;
                 w0 |= (uint32_t)(d0 & 0xff) << (8 * c);

@@ -189,6 +189,13 @@ __device__ __forceinline__ float ldg_f1_hint(const float *p, uint64_t policy) {
     return v;
 }
 
+// rint(v) as an int for |v| < 2^22, without the conversion unit: adding 1.5 * 2^23 leaves the
+// integer, rounded half to even like cvt.rni, in the low mantissa bits.  (F2I and FRND issue at a
+// quarter of the ALU rate on B200 and were the limit of the quantize kernel.)
+__device__ __forceinline__ int rint_small(float v) {
+    return __float_as_int(__fadd_rn(v, 12582912.0f)) - 0x4B400000;
+}
+
 // Programmatic dependent launch: wait for the grids this one depends on / let dependents start.
 __device__ __forceinline__ void grid_dependency_wait() {
     asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -27,16 +27,19 @@ __device__ __forceinline__ float scale_from_max(float max_abs) {
     return (max_abs > 0.0f) ? __fdiv_rn(max_abs, 127.0f) : 1.0f;
 }
 
-// round-half-away-from-zero, clamp to the int8 range, NaN -> 0 (Rust `as i8` semantics).
+// round-half-away-from-zero, clamp to the int8 range, NaN -> 0 (Rust `as i8` semantics), in ALU
+// instructions only.  Clamping first gives the same code as clamping after the rounding and puts
+// the value in the range of the magic-number rounding: u = c + 1.5 * 2^23 holds rint(c), half to
+// even, in its low mantissa bits.  d = c - rint(c) is exact and is +-0.5 only on a tie; half-to-even
+// went TOWARD zero on that tie exactly when d has the sign of c, and then the code steps one away.
 __device__ __forceinline__ int quant_code(float v, float inv_scale) {
-    float t = __fmul_rn(v, inv_scale);
-    float a = fabsf(t);
-    float fl = floorf(a);
-    // a - fl is exact (both are multiples of ulp(a) and the difference is < 1).
-    if (__fsub_rn(a, fl) >= 0.5f) fl = __fadd_rn(fl, 1.0f);
-    float r = copysignf(fl, t);
-    r = fminf(fmaxf(r, -128.0f), 127.0f);
-    return (t != t) ? 0 : (int)r;
+    const float t = __fmul_rn(v, inv_scale);
+    const float c = fminf(fmaxf(t, -128.0f), 127.0f);  // a NaN becomes -128 here and 0 at the end
+    const float u = __fadd_rn(c, 12582912.0f);
+    int r = __float_as_int(u) - 0x4B400000;
+    const float d = __fsub_rn(c, __fsub_rn(u, 12582912.0f));
+    if (fabsf(d) == 0.5f && (__float_as_int(d) ^ __float_as_int(c)) >= 0) r += (c > 0.0f) ? 1 : -1;
+    return (t != t) ? 0 : r;
 }
 
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {

@@ -495,7 +495,7 @@ skinny_prepass_kernel(const __grid_constant__ SkInput one, const SkInput *__rest
         uint32_t w0 = 0u, w1 = 0u, w2 = 0u;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const int v = bad ? 0 : __float2int_rn(xv[b] * f1 * f2);
+            const int v = bad ? 0 : rint_small(xv[b] * f1 * f2);  // |v| <= 2^20
             const int d0 = ((v + 64) & 127) - 64;
             const int v1 = (v - d0) >> 7;
             const int d1 = ((v1 + 64) & 127) - 64;

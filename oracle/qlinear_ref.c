@@ -8,8 +8,11 @@
  * PARITY UNPINNED: the reference is a Rust crate, no Rust toolchain exists where this is
  * built, and the reference's own tests for this path (tests/nn/quantization_tests.rs) hold
  * no golden vectors, only statistical thresholds on unseeded random inputs.  The pins that do
- * exist are (1) those four thresholds, replayed on seeded inputs by the CPU test-suite, and
- * (2) an independent numpy restatement of the quantize step that must agree byte for byte.
+ * exist are (1) those four thresholds, replayed on seeded inputs by the CPU test-suite,
+ * (2) an independent numpy restatement of the quantize step that must agree byte for byte, and
+ * (3) an independent numpy restatement of the forward's AVX2 dot product (lane order, horizontal
+ * sums, scalar tail, with an exactly emulated fused multiply-add) that must agree bit for bit.
+ * Two restatements that agree are still not the reference running: parity stays unpinned.
  *
  * Each function cites the reference lines it follows (path within the reference project).
  *
