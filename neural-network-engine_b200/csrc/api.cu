@@ -134,8 +134,13 @@ int pick_kernel(const nne_qlinear *ql, size_t m, const float *x, const float *y)
     return 3;
 }
 
+// Does a forward of m rows on this layer take a kernel that can store into the peers' windows itself?
+bool forward_stores_to_peers(const nne_qlinear *ql, size_t m, const float *x, const float *y) {
+    return ql->k != 0 && pick_kernel(ql, m, x, y) == 2 && !prefill_bf16_forced();
+}
+
 int forward_dev(nne_qlinear *ql, const float *x, size_t m, size_t k, float *y, size_t ldy,
-                cudaStream_t s) {
+                cudaStream_t s, const PeerSet *peers = nullptr) {
     NNE_TRY(check_layer(ql));
     if (k != ql->k)
         return fail(NNE_ERR_SHAPE_MISMATCH, "shape mismatch: expected [%zu], got [%zu]", ql->k, k);
@@ -152,7 +157,7 @@ int forward_dev(nne_qlinear *ql, const float *x, size_t m, size_t k, float *y, s
     }
     switch (pick_kernel(ql, m, x, y)) {
         case 2:
-            if (!prefill_bf16_forced()) return launch_prefill_i8(ql, x, y, m, ldy, s);
+            if (!prefill_bf16_forced()) return launch_prefill_i8(ql, x, y, m, ldy, s, peers);
             return launch_prefill(ql, x, y, m, ldy, s);
         case 4:
             return launch_skinny(ql, x, y, m, ldy, s);
@@ -834,7 +839,8 @@ int plan_compute(nne_plan *plan, const PeerSet *peers, cudaStream_t s) {
     } else {
         for (size_t i = 0; i < plan->layers.size(); ++i)
             NNE_TRY(forward_dev(plan->layers[i], plan->x[i], plan->m, plan->layers[i]->k, plan->y[i],
-                                plan->ldy[i], s));
+                                plan->ldy[i], s,
+                                (peers && !plan->stores_itself.empty() && plan->stores_itself[i]) ? peers : nullptr));
     }
     for (const nne_plan::PostOp &op : plan->post_ops)
         NNE_TRY(launch_add(plan->ctx, op.y, op.residual, op.count, op.y, s));
@@ -853,8 +859,12 @@ int plan_issue(nne_plan *plan, cudaStream_t s) {
             const PeerSet ps = shard_peerset(g, epoch);
             return plan_compute(plan, &ps, s);
         }
-        NNE_TRY(plan_compute(plan, nullptr, s));
-        return shard_push(g, plan->segs_dev, (int)plan->layers.size(), plan->push_floats, epoch, s);
+        // tensor-core forwards store their tiles into every window themselves; what is left (small
+        // batches, odd shapes) is copied out by the push kernel
+        const PeerSet ps = shard_peerset(g, epoch);
+        NNE_TRY(plan_compute(plan, &ps, s));
+        if (plan->seg_count == 0) return NNE_OK;
+        return shard_push(g, plan->segs_dev, plan->seg_count, plan->push_floats, epoch, s);
     }
     // NCCL route.  One row (or a world of one column block each): the slices already sit where an
     // in-place all-gather of y_full wants them.  More rows: gather [m, width] blocks into a staging
@@ -992,19 +1002,30 @@ int nne_qlinear_plan_create_sharded(nne_shard_group *group, size_t count, nne_ql
         plan->n_total.assign(n_total, n_total + count);
         plan->row_begin.assign(row_begin, row_begin + count);
         if (route == 0 && !plan->fused) {
-            std::vector<PushSeg> segs(count);
+            std::vector<PushSeg> segs;
+            plan->stores_itself.assign(count, 0);
             for (size_t i = 0; i < count; ++i) {
-                segs[i].y = y_slice[i];
-                segs[i].ldy = ldy[i];
-                segs[i].rows = (unsigned)m;
-                segs[i].width = (unsigned)shards[i]->n;
-                segs[i].vec = aligned(y_slice[i], 16) && ldy[i] % 4 == 0 && shards[i]->n % 4 == 0;
+                if (!plan->skinny && plan->pre_ops.empty() && plan->post_ops.empty() &&
+                    forward_stores_to_peers(shards[i], m, plan->x[i], y_slice[i])) {
+                    plan->stores_itself[i] = 1;
+                    continue;
+                }
+                PushSeg sg;
+                sg.y = y_slice[i];
+                sg.ldy = ldy[i];
+                sg.rows = (unsigned)m;
+                sg.width = (unsigned)shards[i]->n;
+                sg.vec = aligned(y_slice[i], 16) && ldy[i] % 4 == 0 && shards[i]->n % 4 == 0;
+                segs.push_back(sg);
                 plan->push_floats += m * shards[i]->n;
             }
-            cudaError_t e = cudaMalloc(&plan->segs_dev, count * sizeof(PushSeg));
-            if (e == cudaSuccess)
-                e = cudaMemcpy(plan->segs_dev, segs.data(), count * sizeof(PushSeg), cudaMemcpyHostToDevice);
-            if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "plan upload failed: %s", cudaGetErrorString(e));
+            plan->seg_count = (int)segs.size();
+            if (!segs.empty()) {
+                cudaError_t e = cudaMalloc(&plan->segs_dev, segs.size() * sizeof(PushSeg));
+                if (e == cudaSuccess)
+                    e = cudaMemcpy(plan->segs_dev, segs.data(), segs.size() * sizeof(PushSeg), cudaMemcpyHostToDevice);
+                if (e != cudaSuccess) st = fail(NNE_ERR_CUDA, "plan upload failed: %s", cudaGetErrorString(e));
+            }
         }
         if (route == 1 && m > 1) {
             cudaError_t e = cudaMalloc(&plan->staging, (size_t)group->world * m * widest * sizeof(float));
@@ -1092,7 +1113,7 @@ int nne_qlinear_plan_launches(const nne_plan *plan) {
     if (!plan) return 0;
     if (plan->fused) return 1;
     const int extra = (int)(plan->pre_ops.size() + plan->post_ops.size());
-    const int push = extra + ((plan->group && plan->group->world > 1 && plan->route == 0) ? 1 : 0);  // + slice push kernel
+    const int push = extra + ((plan->group && plan->group->world > 1 && plan->route == 0 && plan->seg_count) ? 1 : 0);  // + slice push kernel
     if (plan->skinny) return 2 + push;  // pre-pass + kernel
     return (int)plan->layers.size() + push;
 }

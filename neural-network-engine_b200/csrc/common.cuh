@@ -134,6 +134,7 @@ inline int use_ctx(const nne_ctx *ctx) {
 }
 
 // kernels' host launchers (defined next to the kernels) ---------------------------------------
+struct PeerSet;  // shard.cuh: the other ranks' windows, for a column shard's launch
 int launch_quantize_rows(nne_ctx *ctx, const float *w, size_t rows, size_t cols, int8_t *q,
                          float *scales, cudaStream_t s);
 int launch_quantize_tensor(nne_ctx *ctx, const float *v, size_t n, int8_t *q, float *scale_dev,
@@ -178,7 +179,6 @@ int launch_gemv_tma(nne_ctx *ctx, const int8_t *q, const float *scales, const fl
 int launch_gemv_tma_passes(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                            const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                            cudaStream_t s);
-struct PeerSet;  // shard.cuh: the other ranks' windows, for a column shard's launch
 int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
                         size_t m, bool reuse, cudaStream_t s, const PeerSet *peers = nullptr);
 int launch_generic(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
@@ -210,7 +210,7 @@ bool prefill_i8_supports(const nne_qlinear *ql, size_t m);
 int prefill_i8_prepare_layer(nne_qlinear *ql);
 void prefill_i8_release_layer(nne_qlinear *ql);
 int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
-                      cudaStream_t s);
+                      cudaStream_t s, const PeerSet *peers = nullptr);
 
 }  // namespace nne
 
@@ -256,6 +256,8 @@ struct nne_plan {
     std::vector<float *> y_full;      // [m, n_total[i]] in this rank's window
     std::vector<size_t> n_total, row_begin;
     nne::PushSeg *segs_dev = nullptr; // the slices to copy out when the forward kernels do not do it themselves
+    int seg_count = 0;
+    std::vector<char> stores_itself;  // per layer: its forward kernel stores into every window
     size_t push_floats = 0;
     float *staging = nullptr;         // NCCL route, m > 1: [world][m][width] of the widest layer
 };

@@ -28,6 +28,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "shard.cuh"
 
 namespace nne {
 namespace {
@@ -99,14 +100,18 @@ struct Bars {
 };
 static_assert(sizeof(Bars) <= BAR_BYTES, "barrier block too large");
 
-template <int BN>
+// PEER (column shards): the epilogue stores every output tile into this rank's window and, through
+// the peer mappings, into the other ranks' windows - the all-gather of the output slices happens
+// tile by tile under the MMAs of the following tiles (TMEM is handed back before anything is
+// stored), instead of as a copy of the whole slice after the kernel.  Plain stores only.
+template <int BN, bool PEER>
 __global__ void __launch_bounds__(THREADS, 1)
 qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                           const __grid_constant__ CUtensorMap tmap_x0,
                           const __grid_constant__ CUtensorMap tmap_x1,
                           const float *__restrict__ unscale, const float *__restrict__ scales,
                           const float *__restrict__ bias, float *__restrict__ y, int m, int n, int k,
-                          size_t ldy, int tiles_m, int num_tiles, int *err) {
+                          size_t ldy, int tiles_m, int num_tiles, int *err, const PeerSet ps) {
     constexpr int STAGES = Cfg<BN>::STAGES, W_BYTES = Cfg<BN>::W_BYTES,
                   STAGE_BYTES = Cfg<BN>::STAGE_BYTES;
     constexpr uint32_t TMEM_COLS = Cfg<BN>::TMEM_COLS, IDESC = Cfg<BN>::IDESC;
@@ -304,8 +309,16 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                             o.z = __fadd_rn(o.z, bv.z);
                             o.w = __fadd_rn(o.w, bv.w);
                         }
-                        if (row0 + rr < m)
-                            *reinterpret_cast<float4 *>(y + (size_t)(row0 + rr) * ldy + j0 + 4 * c4) = o;
+                        if (row0 + rr < m) {
+                            float4 *dst = reinterpret_cast<float4 *>(y + (size_t)(row0 + rr) * ldy + j0 + 4 * c4);
+                            *dst = o;
+                            if (PEER) {
+#pragma unroll
+                                for (int q = 0; q < SHARD_MAX_RANKS; ++q)
+                                    if (q < ps.world && q != ps.rank)
+                                        *reinterpret_cast<float4 *>(reinterpret_cast<char *>(dst) + ps.delta[q]) = o;
+                            }
+                        }
                     }
                     __syncwarp();  // the block is rewritten by the next chunk
                 } else if (row < m) {
@@ -317,6 +330,12 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
                             float o = __fmul_rn(f[ci * 32 + v] * us, __ldg(scales + j));
                             if (bias) o = __fadd_rn(o, __ldg(bias + j));
                             yrow[j] = o;
+                            if (PEER) {
+#pragma unroll
+                                for (int q = 0; q < SHARD_MAX_RANKS; ++q)
+                                    if (q < ps.world && q != ps.rank)
+                                        *reinterpret_cast<float *>(reinterpret_cast<char *>(yrow + j) + ps.delta[q]) = o;
+                            }
                         }
                     }
                 }
@@ -581,11 +600,28 @@ void prefill_i8_release_layer(nne_qlinear *ql) {
     ql->tmap_w8 = nullptr;
 }
 
+namespace {
+template <int BN, bool PEER>
+cudaError_t launch_main(const cudaLaunchConfig_t &cfg, const CUtensorMap &map_w, const CUtensorMap &x0,
+                        const CUtensorMap &x1, const float *unscale, const nne_qlinear *ql, float *y, size_t m,
+                        size_t ldy, int tiles_m, int tiles, int *err, const PeerSet &ps) {
+    return cudaLaunchKernelEx(&cfg, qlinear_prefill_i8_kernel<BN, PEER>, map_w, x0, x1, unscale,
+                              (const float *)ql->scales, (const float *)ql->bias, y, (int)m, (int)ql->n,
+                              (int)ql->k, ldy, tiles_m, tiles, err, ps);
+}
+}  // namespace
+
 int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_t ldy,
-                      cudaStream_t s) {
+                      cudaStream_t s, const PeerSet *peers) {
     nne_ctx *ctx = ql->ctx;
-    NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<256>, Cfg<256>::SMEM_BYTES));
-    NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<128>, Cfg<128>::SMEM_BYTES));
+    const bool peer = peers && peers->world > 1;
+    if (peer) {
+        NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<256, true>, Cfg<256>::SMEM_BYTES));
+        NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<128, true>, Cfg<128>::SMEM_BYTES));
+    } else {
+        NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<256, false>, Cfg<256>::SMEM_BYTES));
+        NNE_TRY(ensure_dynamic_smem(ctx->device, qlinear_prefill_i8_kernel<128, false>, Cfg<128>::SMEM_BYTES));
+    }
     // stream-ordered workspace: two int8 digit planes [m, k] and the per-row factors [m]
     const size_t plane = m * ql->k;
     const size_t bytes = 2 * plane + ((m * sizeof(float) + 255) & ~(size_t)255) + 256;
@@ -663,17 +699,21 @@ int launch_prefill_i8(nne_qlinear *ql, const float *x, float *y, size_t m, size_
     cfg.stream = s;
     cfg.attrs = pdl;
     cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    const PeerSet none;
+    const PeerSet &ps = peer ? *peers : none;
+    // the 128-row boxes are the small-batch kernel's tensor map of q
+    const CUtensorMap &map_w = *static_cast<const CUtensorMap *>(narrow ? ql->tmap_wsk : ql->tmap_w8);
     cudaError_t e;
-    if (narrow)  // the 128-row boxes are the small-batch kernel's tensor map of q
-        e = cudaLaunchKernelEx(&cfg, qlinear_prefill_i8_kernel<128>,
-                               *static_cast<const CUtensorMap *>(ql->tmap_wsk), tmap_x0, tmap_x1,
-                               (const float *)unscale, (const float *)ql->scales, (const float *)ql->bias,
-                               y, (int)m, (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
+    if (narrow)
+        e = peer ? launch_main<128, true>(cfg, map_w, tmap_x0, tmap_x1, unscale, ql, y, m, ldy, tiles_m, (int)tiles,
+                                          ctx->err_word, ps)
+                 : launch_main<128, false>(cfg, map_w, tmap_x0, tmap_x1, unscale, ql, y, m, ldy, tiles_m, (int)tiles,
+                                           ctx->err_word, ps);
     else
-        e = cudaLaunchKernelEx(&cfg, qlinear_prefill_i8_kernel<256>,
-                               *static_cast<const CUtensorMap *>(ql->tmap_w8), tmap_x0, tmap_x1,
-                               (const float *)unscale, (const float *)ql->scales, (const float *)ql->bias,
-                               y, (int)m, (int)ql->n, (int)ql->k, ldy, tiles_m, (int)tiles, ctx->err_word);
+        e = peer ? launch_main<256, true>(cfg, map_w, tmap_x0, tmap_x1, unscale, ql, y, m, ldy, tiles_m, (int)tiles,
+                                          ctx->err_word, ps)
+                 : launch_main<256, false>(cfg, map_w, tmap_x0, tmap_x1, unscale, ql, y, m, ldy, tiles_m, (int)tiles,
+                                           ctx->err_word, ps);
     count_launch();
     cudaFreeAsync(ws, s);
     if (e != cudaSuccess)

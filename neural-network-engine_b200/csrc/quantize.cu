@@ -27,24 +27,29 @@ __device__ __forceinline__ float scale_from_max(float max_abs) {
     return (max_abs > 0.0f) ? __fdiv_rn(max_abs, 127.0f) : 1.0f;
 }
 
-// round-half-away-from-zero, clamp to the int8 range, NaN -> 0 (Rust `as i8` semantics), in ALU
-// instructions only.  Clamping first gives the same code as clamping after the rounding and puts
-// the value in the range of the magic-number rounding: u = c + 1.5 * 2^23 holds rint(c), half to
-// even, in its low mantissa bits.  d = c - rint(c) is exact and is +-0.5 only on a tie; half-to-even
-// went TOWARD zero on that tie exactly when d has the sign of c, and then the code steps one away.
+// round-half-away-from-zero, clamp to the int8 range, NaN -> 0 (Rust `as i8` semantics), without
+// the conversion unit and with as few ALU-pipe instructions (min/max, compare, select, logic) as
+// could be found - the kernel is bound by that pipe, not by HBM.  Clamping first gives the same code
+// as clamping after the rounding and puts the value in the range of the magic-number rounding:
+// u = c + 1.5 * 2^23 holds rint(c), half to even, in its low mantissa bits and u - 1.5 * 2^23 is
+// that integer as a float.  d = c - rint(c) is exact and equals copysign(0.5, c) exactly when c is
+// a tie that half-to-even sent TOWARD zero; the code then steps one away (in float, where the step
+// is 2 d).  The last magic add turns the integer-valued float back into an int.
 __device__ __forceinline__ int quant_code(float v, float inv_scale) {
-    const float t = __fmul_rn(v, inv_scale);
-    const float c = fminf(fmaxf(t, -128.0f), 127.0f);  // a NaN becomes -128 here and 0 at the end
-    const float u = __fadd_rn(c, 12582912.0f);
-    int r = __float_as_int(u) - 0x4B400000;
-    const float d = __fsub_rn(c, __fsub_rn(u, 12582912.0f));
-    if (fabsf(d) == 0.5f && (__float_as_int(d) ^ __float_as_int(c)) >= 0) r += (c > 0.0f) ? 1 : -1;
-    return (t != t) ? 0 : r;
+    float t = __fmul_rn(v, inv_scale);
+    t = (t == t) ? t : 0.0f;
+    const float c = fminf(fmaxf(t, -128.0f), 127.0f);
+    const float rf = __fsub_rn(__fadd_rn(c, 12582912.0f), 12582912.0f);
+    const float d = __fsub_rn(c, rf);
+    const float half = copysignf(0.5f, c);
+    const float r = (d == half) ? __fadd_rn(rf, __fadd_rn(half, half)) : rf;
+    return __float_as_int(__fadd_rn(r, 12582912.0f)) - 0x4B400000;
 }
 
+// Four codes -> one word, low byte first.
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) |
-           ((uint32_t)(d & 0xff) << 24);
+    return __byte_perm(__byte_perm((uint32_t)a, (uint32_t)b, 0x0040), __byte_perm((uint32_t)c, (uint32_t)d, 0x0040),
+                       0x5410);
 }
 
 __device__ __forceinline__ float warp_max(float m) {
