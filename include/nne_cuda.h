@@ -294,7 +294,9 @@ NNE_API int nne_qlinear_plan_create_fused(nne_ctx *ctx, size_t count, const nne_
  *            on the run's stream; needs equal slices in rank order.  m = 1 gathers in place; m > 1
  *            gathers [m, width] blocks into a staging area and interleaves them into row-major
  *            [m, n_total].  nne_shard_group_wait is not needed (and harmless).
- * Rules, as for collectives: all ranks issue the same sequence of sharded runs on a group.  A rank
+ * Rules, as for collectives: all ranks issue the same sequence of sharded runs and waits on a
+ * group, and a rank issues them on ONE stream (or orders them with events): a run announces the
+ * rank's previous run as complete.  A rank
  * may overwrite an output area only when every peer has finished reading what it held: with run,
  * wait and the reads in ONE stream two alternating areas are enough ("a peer has signalled run e+1"
  * implies "it has read run e"); a caller that keeps d runs in flight before it waits needs 2 d areas.
@@ -316,6 +318,8 @@ NNE_API int nne_shard_group_wait(nne_shard_group *group, void *stream);
 /* ncclComm_t (as void*) of this rank, created by the host, for route 1.  The library calls the
  * NCCL copy the process has loaded (or the one NNE_NCCL_LIB names); it does not link NCCL. */
 NNE_API int nne_shard_group_set_nccl(nne_shard_group *group, void *nccl_comm);
+/* Unmaps the peers' windows and frees this rank's.  Call it when no rank can still store into this
+ * window or read a mapping of it (after a barrier of the host's own making). */
 NNE_API int nne_shard_group_destroy(nne_shard_group *group);
 /* A plan over column shards: shards[i] holds rows [row_begin[i], row_begin[i] + shards[i].n) of a
  * layer with n_total[i] output channels; x_dev[i] is [m, k_i] (replicated on every rank, anywhere

@@ -154,6 +154,12 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
                                               const float *bias_s, bool staged, int lane,
                                               uint32_t empty_bar, const PeerSet &ps) {
     const int k = L.k;
+    // The residual of the output this lane will finish, fetched now so that its latency passes
+    // under the dot products instead of behind them.
+    const float *residual = lc->residual;
+    float res = 0.0f;
+    if (residual && lane < rows * MT)
+        res = residual[(size_t)(lane % MT) * L.ldy + row0 + jl0 + lane / MT];
     int acc[RW][MT][3];
 #pragma unroll
     for (int r = 0; r < RW; ++r)
@@ -207,8 +213,7 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
         const float sc = staged ? scale_s[jl] : __ldg(L.scales + row0 + jl);
         float val = __fmul_rn(dot, sc);
         if (L.bias) val = __fadd_rn(val, staged ? bias_s[jl] : __ldg(L.bias + row0 + jl));
-        const float *residual = lc->residual;
-        if (residual) val = __fadd_rn(val, residual[(size_t)m * L.ldy + row0 + jl]);
+        if (residual) val = __fadd_rn(val, res);
         store_result<PEER>(L.y + (size_t)m * L.ldy + row0 + jl, val, ps);
     }
 }
@@ -259,6 +264,26 @@ __device__ __noinline__ void consume_stage_fp32(const StreamLayer &L, const uint
     if (lane == 31) mbar_arrive(empty_bar);
 }
 
+// Four consecutive elements of row m of x', starting at column col (a multiple of 4), from the raw
+// x values: the auxiliary operand (gamma or x2) comes in one 16-byte load.  Both are 16-byte aligned
+// (checked when the plan is built).
+__device__ __forceinline__ float4 input_value4(const StreamLayer &L, float4 t, int m, size_t col, float rrms) {
+    if (L.gamma) {
+        const float4 g = __ldg(reinterpret_cast<const float4 *>(L.gamma + col));
+        t.x = __fmul_rn(__fmul_rn(t.x, rrms), g.x);
+        t.y = __fmul_rn(__fmul_rn(t.y, rrms), g.y);
+        t.z = __fmul_rn(__fmul_rn(t.z, rrms), g.z);
+        t.w = __fmul_rn(__fmul_rn(t.w, rrms), g.w);
+    } else if (L.x2) {
+        const float4 u = *reinterpret_cast<const float4 *>(L.x2 + (size_t)m * L.k + col);
+        t.x = __fmul_rn(__fdiv_rn(t.x, __fadd_rn(1.0f, expf(-t.x))), u.x);
+        t.y = __fmul_rn(__fdiv_rn(t.y, __fadd_rn(1.0f, expf(-t.y))), u.y);
+        t.z = __fmul_rn(__fdiv_rn(t.z, __fadd_rn(1.0f, expf(-t.z))), u.z);
+        t.w = __fmul_rn(__fdiv_rn(t.w, __fadd_rn(1.0f, expf(-t.w))), u.w);
+    }
+    return t;
+}
+
 // Prep-warp passes over a layer's activations.  XF = the layer has an input transform; the plain
 // case is kept free of it (a test per element in these loops showed up as 4 % of a 12-layer launch).
 // Pass 1: max |x'| per row and the Inf/NaN flag.
@@ -274,13 +299,7 @@ __device__ __forceinline__ void prep_scan(const StreamLayer &L, int ptid, int ch
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
                 float4 t4 = ld_f4_hint(p4 + v, pol_keep);
-                if (XF) {
-                    const size_t col = (size_t)c * 16 + 4 * v;
-                    t4.x = input_value(L, t4.x, m, col + 0, rr[m]);
-                    t4.y = input_value(L, t4.y, m, col + 1, rr[m]);
-                    t4.z = input_value(L, t4.z, m, col + 2, rr[m]);
-                    t4.w = input_value(L, t4.w, m, col + 3, rr[m]);
-                }
+                if (XF) t4 = input_value4(L, t4, m, (size_t)c * 16 + 4 * v, rr[m]);
                 const float a0 = fabsf(t4.x), a1 = fabsf(t4.y), a2 = fabsf(t4.z), a3 = fabsf(t4.w);
                 bad |= !(a0 <= 3.402823466e38f) | !(a1 <= 3.402823466e38f) |
                        !(a2 <= 3.402823466e38f) | !(a3 <= 3.402823466e38f);
@@ -304,21 +323,80 @@ __device__ __forceinline__ void prep_digits(const StreamLayer &L, int m, int pti
             float xv[16];
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
-                const float4 t4 = p4[v];
+                float4 t4 = p4[v];
+                if (XF) t4 = input_value4(L, t4, m, (size_t)c * 16 + 4 * v, rr);
                 xv[4 * v + 0] = t4.x;
                 xv[4 * v + 1] = t4.y;
                 xv[4 * v + 2] = t4.z;
                 xv[4 * v + 3] = t4.w;
-            }
-            if (XF) {
-#pragma unroll
-                for (int v = 0; v < 16; ++v) xv[v] = input_value(L, xv[v], m, (size_t)c * 16 + v, rr);
             }
             chunk_digits(xv, f1, f2, o0, o1, o2);
         }
         plane[c] = o0;
         plane[kpad + c] = o1;
         plane[2 * kpad + c] = o2;
+    }
+}
+
+// One activation row with an input transform, held in registers between the passes: thread ptid
+// keeps chunks ptid, ptid + PREP_THREADS, ... (at most XF_CACHE_CHUNKS of them, i.e. k <= 14336; the
+// host checks).  x and the auxiliary operand are read from global memory once, all loads of a
+// chunk issued before anything is computed on them, and silu - an exp and an IEEE divide per
+// element, in every CTA - is evaluated once instead of once per pass.
+constexpr int XF_CACHE_CHUNKS = 4;
+__device__ __forceinline__ void xf_load(const StreamLayer &L, int ptid, int chunks, uint64_t pol_keep,
+                                        float (&xc)[XF_CACHE_CHUNKS][16]) {
+#pragma unroll
+    for (int u = 0; u < XF_CACHE_CHUNKS; ++u) {
+        const int c = ptid + u * PREP_THREADS;
+        float4 t[4], a[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) t[v] = a[v] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < chunks) {
+            const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)c * 16);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) t[v] = ld_f4_hint(p4 + v, pol_keep);
+            if (L.x2) {
+                const float4 *q4 = reinterpret_cast<const float4 *>(L.x2 + (size_t)c * 16);
+#pragma unroll
+                for (int v = 0; v < 4; ++v) a[v] = ld_f4_hint(q4 + v, pol_keep);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            if (L.x2) {
+                // silu with the fast exponential and divide (each within about 2 ulp): every CTA
+                // evaluates the whole row, and the result goes onto a 2^-20 grid right after
+                t[v].x = __fmul_rn(__fdividef(t[v].x, 1.0f + __expf(-t[v].x)), a[v].x);
+                t[v].y = __fmul_rn(__fdividef(t[v].y, 1.0f + __expf(-t[v].y)), a[v].y);
+                t[v].z = __fmul_rn(__fdividef(t[v].z, 1.0f + __expf(-t[v].z)), a[v].z);
+                t[v].w = __fmul_rn(__fdividef(t[v].w, 1.0f + __expf(-t[v].w)), a[v].w);
+            }
+            xc[u][4 * v + 0] = t[v].x;
+            xc[u][4 * v + 1] = t[v].y;
+            xc[u][4 * v + 2] = t[v].z;
+            xc[u][4 * v + 3] = t[v].w;
+        }
+    }
+}
+__device__ __forceinline__ void xf_apply_gamma(const StreamLayer &L, int ptid, int chunks, float rrms,
+                                               float (&xc)[XF_CACHE_CHUNKS][16]) {
+#pragma unroll
+    for (int u = 0; u < XF_CACHE_CHUNKS; ++u) {
+        const int c = ptid + u * PREP_THREADS;
+        if (c < chunks) {
+            const float4 *g4 = reinterpret_cast<const float4 *>(L.gamma + (size_t)c * 16);
+            float4 g[4];
+#pragma unroll
+            for (int v = 0; v < 4; ++v) g[v] = __ldg(g4 + v);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                xc[u][4 * v + 0] = __fmul_rn(__fmul_rn(xc[u][4 * v + 0], rrms), g[v].x);
+                xc[u][4 * v + 1] = __fmul_rn(__fmul_rn(xc[u][4 * v + 1], rrms), g[v].y);
+                xc[u][4 * v + 2] = __fmul_rn(__fmul_rn(xc[u][4 * v + 2], rrms), g[v].z);
+                xc[u][4 * v + 3] = __fmul_rn(__fmul_rn(xc[u][4 * v + 3], rrms), g[v].w);
+            }
+        }
     }
 }
 
@@ -440,47 +518,79 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
             }
             if (li == 0) grid_dependency_wait();  // x may be the previous kernel's output
 
-            // pass 0 (RMSNorm input only): sum of squares per row -> rrms
+            const bool xform = L.gamma != nullptr || L.x2 != nullptr;
+            const bool cached = MT == 1 && xform;  // one row: x' stays in registers between the passes
+            float xc[XF_CACHE_CHUNKS][16];
             float rr[MT];
 #pragma unroll
             for (int m = 0; m < MT; ++m) rr[m] = 1.0f;
-            if (L.gamma) {
-#pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    float acc = 0.0f;
-                    for (int c = ptid; c < chunks; c += PREP_THREADS) {
-                        const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            const float4 t4 = ld_f4_hint(p4 + v, pol_keep);
-                            acc = fmaf(t4.x, t4.x, acc);
-                            acc = fmaf(t4.y, t4.y, acc);
-                            acc = fmaf(t4.z, t4.z, acc);
-                            acc = fmaf(t4.w, t4.w, acc);
-                        }
-                    }
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                    if (lane == 0) bars->sumsq[li & 1][pwarp][m] = acc;
-                }
-                // sumsq alternates by layer parity, so the previous layer's readers are not disturbed
-                named_bar_sync(1, PREP_THREADS);
-#pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    float tot = 0.0f;
-                    for (int w = 0; w < PREP_WARPS; ++w) tot += bars->sumsq[li & 1][w][m];
-                    rr[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)k), L.eps)));
-                }
-            }
-            const bool xform = L.gamma != nullptr || L.x2 != nullptr;
-
-            // pass 1: max |x'| and the Inf/NaN flag per activation row
             float mx[MT];
             int bad = 0;
-            if (xform)
-                prep_scan<MT, true>(L, ptid, chunks, pol_keep, rr, mx, bad);
-            else
-                prep_scan<MT, false>(L, ptid, chunks, pol_keep, rr, mx, bad);
+            if (cached) {
+                xf_load(L, ptid, chunks, pol_keep, xc);
+                if (L.gamma) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int u = 0; u < XF_CACHE_CHUNKS; ++u)
+#pragma unroll
+                        for (int v = 0; v < 16; ++v) acc = fmaf(xc[u][v], xc[u][v], acc);
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    if (lane == 0) bars->sumsq[li & 1][pwarp][0] = acc;
+                    named_bar_sync(1, PREP_THREADS);
+                    float tot = 0.0f;
+                    for (int w = 0; w < PREP_WARPS; ++w) tot += bars->sumsq[li & 1][w][0];
+                    rr[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)k), L.eps)));
+                    xf_apply_gamma(L, ptid, chunks, rr[0], xc);
+                }
+                float m0 = 0.0f;
+#pragma unroll
+                for (int u = 0; u < XF_CACHE_CHUNKS; ++u)
+#pragma unroll
+                    for (int v = 0; v < 16; ++v) {
+                        const float a0 = fabsf(xc[u][v]);
+                        bad |= !(a0 <= 3.402823466e38f);
+                        m0 = fmaxf(m0, a0);
+                    }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, o));
+                mx[0] = m0;
+            } else {
+                // pass 0 (RMSNorm input only): sum of squares per row -> rrms
+                if (L.gamma) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        float acc = 0.0f;
+                        for (int c = ptid; c < chunks; c += PREP_THREADS) {
+                            const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                const float4 t4 = ld_f4_hint(p4 + v, pol_keep);
+                                acc = fmaf(t4.x, t4.x, acc);
+                                acc = fmaf(t4.y, t4.y, acc);
+                                acc = fmaf(t4.z, t4.z, acc);
+                                acc = fmaf(t4.w, t4.w, acc);
+                            }
+                        }
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                        if (lane == 0) bars->sumsq[li & 1][pwarp][m] = acc;
+                    }
+                    // sumsq alternates by layer parity, so the previous layer's readers are not disturbed
+                    named_bar_sync(1, PREP_THREADS);
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        float tot = 0.0f;
+                        for (int w = 0; w < PREP_WARPS; ++w) tot += bars->sumsq[li & 1][w][m];
+                        rr[m] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)k), L.eps)));
+                    }
+                }
+                // pass 1: max |x'| and the Inf/NaN flag per activation row
+                if (xform)
+                    prep_scan<MT, true>(L, ptid, chunks, pol_keep, rr, mx, bad);
+                else
+                    prep_scan<MT, false>(L, ptid, chunks, pol_keep, rr, mx, bad);
+            }
             bad = __any_sync(0xffffffffu, bad);
             // The buffer (digits, scales, flags) may still be read by math warps working on layer
             // li - num_bufs: wait until all of them have released it.
@@ -525,10 +635,23 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
                         bars->lc[buf].unscale[m][1] = pow2f(-e2);
                     }
                     uint4 *plane = xs + (size_t)m * 3 * kpad;
-                    if (xform)
+                    if (cached) {
+#pragma unroll
+                        for (int u = 0; u < XF_CACHE_CHUNKS; ++u) {
+                            const int c = ptid + u * PREP_THREADS;
+                            if (c < kpad) {  // chunks past the row's end hold zeros
+                                uint4 o0, o1, o2;
+                                chunk_digits(xc[u], f1, f2, o0, o1, o2);
+                                plane[c] = o0;
+                                plane[kpad + c] = o1;
+                                plane[2 * kpad + c] = o2;
+                            }
+                        }
+                    } else if (xform) {
                         prep_digits<true>(L, m, ptid, chunks, kpad, f1, f2, rr[m], plane);
-                    else
+                    } else {
                         prep_digits<false>(L, m, ptid, chunks, kpad, f1, f2, rr[m], plane);
+                    }
                 }
             }
             // publish the buffer to the math warps

@@ -179,8 +179,7 @@ __device__ __forceinline__ float4 ld_f4_hint(const float4 *p, uint64_t policy) {
     float4 v;
     asm volatile("ld.global.L2::cache_hint.v4.f32 {%0,%1,%2,%3}, [%4], %5;"
                  : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(p), "l"(policy)
-                 : "memory");
+                 : "l"(p), "l"(policy));
     return v;
 }
 __device__ __forceinline__ float ldg_f1_hint(const float *p, uint64_t policy) {

@@ -23,6 +23,28 @@ H, F, LAYERS = 4096, 11008, 32
 NAMES = [("q", H, H), ("k", H, H), ("v", H, H), ("o", H, H), ("gate", F, H), ("up", F, H), ("down", H, F)]
 
 
+def graph_time_ms(torch, issue, reps=5):
+    """Device time of one replay of a CUDA graph holding everything `issue(stream)` launches: the
+    chain as the GPU runs it, without the host's per-launch cost (Python + ctypes, about as long as
+    a decode-sized kernel)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        issue(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
 def test_config4_decoder_stack(nne, ctx):
     import torch
     lib = nne.load()
@@ -139,10 +161,94 @@ def test_config4_decoder_stack(nne, ctx):
         t0 = time.perf_counter()
         plan_step()
         dt = time.perf_counter() - t0
-        print(f"config4 batch {b}, grouped into plans: {dt * 1e3:.2f} ms per decode step, "
-              f"{b / dt:.0f} tokens/s, {total_bytes / dt / 1e9:.0f} GB/s of weights")
+        # (the graph resets the hidden state like plan_step does: fed its own output again and again,
+        # a chain without norms overflows to Inf and every forward takes the kernels' IEEE slow path)
+        gms = graph_time_ms(torch, lambda st: [hid[0].copy_(xb)] + [lib.nne_qlinear_plan_run(p, st) for p in plans])
+        print(f"config4 batch {b}, grouped into plans: {dt * 1e3:.2f} ms per decode step issued from "
+              f"Python, {gms:.3f} ms as a CUDA graph ({b / gms * 1e3:.0f} tokens/s, "
+              f"{total_bytes / gms / 1e6:.0f} GB/s of weights)")
         for p in plans:
             lib.nne_qlinear_plan_destroy(p)
+    # The same stack as a chain of decoder BLOCKS with the element-wise steps of the reference's
+    # Llama2Block (src/models/llama.rs:377-392; attention itself is not part of this path, v stands
+    # in for its output): q/k/v read RMSNorm(h), o adds the residual h, gate/up read RMSNorm(h2),
+    # down reads silu(gate) * up and adds the residual h2.  (a) fused plans: at batch 1 every launch
+    # is the decode kernel, nothing else runs between layers; (b) the same steps as standalone
+    # kernels around plain plans.  Batch 8 must agree bit for bit (the fused plan runs the very same
+    # kernels), batch 1 within 1e-3 of the hidden state's size after 32 layers (rrms is summed in
+    # another order inside the decode kernel).
+    g_attn = [torch.ones(H, device=dev) + 0.05 * torch.randn(H, generator=gen, device=dev) for _ in range(LAYERS)]
+    g_ffn = [torch.ones(H, device=dev) + 0.05 * torch.randn(H, generator=gen, device=dev) for _ in range(LAYERS)]
+    eps = 1e-5
+    for b in (1, 8):
+        xb = x8[:b].contiguous()
+        bufs = {name: torch.empty(b, n, device=dev) for name, n, _ in NAMES}
+        hid = [torch.empty(b, H, device=dev), torch.empty(b, H, device=dev)]
+        h2 = torch.empty(b, H, device=dev)
+        norm, act = torch.empty(b, H, device=dev), torch.empty(b, F, device=dev)
+        fused = []
+        for li, layer in enumerate(stack):
+            src, dst = hid[li % 2], hid[(li + 1) % 2]
+            L = {nm: type("L", (), {"_live_handle": (lambda self, h=layer[nm]: h), "_ctx": ctx})() for nm, _, _ in NAMES}
+            ga, gf = g_attn[li].data_ptr(), g_ffn[li].data_ptr()
+            fused.append(nne.FusedPlan([{"layer": L[nm], "x": src.data_ptr(), "y": bufs[nm].data_ptr(),
+                                         "rmsnorm": (ga, eps)} for nm in ("q", "k", "v")], b, ctx))
+            fused.append(nne.FusedPlan([{"layer": L["o"], "x": bufs["v"].data_ptr(), "y": h2.data_ptr(),
+                                         "residual": src.data_ptr()}], b, ctx))
+            fused.append(nne.FusedPlan([{"layer": L[nm], "x": h2.data_ptr(), "y": bufs[nm].data_ptr(),
+                                         "rmsnorm": (gf, eps)} for nm in ("gate", "up")], b, ctx))
+            fused.append(nne.FusedPlan([{"layer": L["down"], "x": bufs["gate"].data_ptr(), "y": dst.data_ptr(),
+                                         "silu_mul": bufs["up"].data_ptr(), "residual": h2.data_ptr()}], b, ctx))
+        launches = sum(p.launches for p in fused)
+
+        def fused_step():
+            hid[0].copy_(xb)
+            for p in fused:
+                p.run(stream)
+            torch.cuda.synchronize()
+            return hid[LAYERS % 2].clone()
+
+        def unfused_step():
+            hid[0].copy_(xb)
+            for li, layer in enumerate(stack):
+                src, dst = hid[li % 2], hid[(li + 1) % 2]
+                nne.rmsnorm_device(ctx, src.data_ptr(), g_attn[li].data_ptr(), eps, b, H, norm.data_ptr(), stream)
+                for nm in ("q", "k", "v"):
+                    fwd(layer[nm], norm, b, H, bufs[nm])
+                fwd(layer["o"], bufs["v"], b, H, h2)
+                nne.add_device(ctx, h2.data_ptr(), src.data_ptr(), b * H, h2.data_ptr(), stream)
+                nne.rmsnorm_device(ctx, h2.data_ptr(), g_ffn[li].data_ptr(), eps, b, H, norm.data_ptr(), stream)
+                fwd(layer["gate"], norm, b, H, bufs["gate"])
+                fwd(layer["up"], norm, b, H, bufs["up"])
+                nne.silu_mul_device(ctx, bufs["gate"].data_ptr(), bufs["up"].data_ptr(), b * F, act.data_ptr(), stream)
+                fwd(layer["down"], act, b, F, dst)
+                nne.add_device(ctx, dst.data_ptr(), h2.data_ptr(), b * H, dst.data_ptr(), stream)
+            torch.cuda.synchronize()
+            return hid[LAYERS % 2].clone()
+
+        want = unfused_step()
+        got = fused_step()
+        ctx.check()
+        assert bool(torch.isfinite(got).all()) and bool(torch.isfinite(want).all())
+        rel = float((got - want).abs().max() / want.abs().max())
+        if b == 8:
+            assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+        else:
+            assert rel <= 1e-3, rel
+        t0 = time.perf_counter()
+        fused_step()
+        dt_f = time.perf_counter() - t0
+        t0 = time.perf_counter()
+        unfused_step()
+        dt_u = time.perf_counter() - t0
+        gms = graph_time_ms(torch, lambda st: [hid[0].copy_(xb)] + [p.run(st) for p in fused])
+        print(f"config4 batch {b}, decoder blocks with RMSNorm / SiLU*mul / residuals: fused plans "
+              f"{dt_f * 1e3:.2f} ms issued from Python, {gms:.3f} ms as a CUDA graph ({launches} launches, "
+              f"{b / gms * 1e3:.0f} tokens/s, {total_bytes / gms / 1e6:.0f} GB/s of weights); standalone "
+              f"element-wise kernels + one forward per layer {dt_u * 1e3:.2f} ms from Python; "
+              f"max |diff| / max |h| = {rel:.2e}")
+        for p in fused:
+            p.close()
     # The 224 layers as INDEPENDENT forwards, each fed its own N(0,1) activation, all in one plan:
     # tokens/s = batch / time of the 224 forwards.
     flat = [(layer[name], n, k) for layer in stack for name, n, k in NAMES]
