@@ -727,10 +727,8 @@ int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *l
         fused = aligned(ql->q, 16) && aligned(x_dev_in[i], 16) && aligned(y_dev[i], 4) &&
                 gemv_tma_supports(ql->n, ql->k, m) &&
                 !(m >= 2 && !skinny_disabled() && ql->tmap_wsk) &&
-                // the decode kernel reads gamma and x2 sixteen bytes at a time and, for one row, keeps
-                // a transformed row of at most 14336 elements in its prep warps' registers
-                (!items || (aligned(items[i].gamma, 16) && aligned(items[i].x2, 16) &&
-                            (items[i].input_op == NNE_INPUT_PLAIN || m > 1 || ql->k <= 14336)));
+                // the decode kernel reads gamma and x2 sixteen bytes at a time
+                (!items || (aligned(items[i].gamma, 16) && aligned(items[i].x2, 16)));
     }
     std::vector<const float *> x_eff(x_dev_in, x_dev_in + count);
     if (items && !fused) {

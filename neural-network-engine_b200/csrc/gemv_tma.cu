@@ -154,12 +154,6 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
                                               const float *bias_s, bool staged, int lane,
                                               uint32_t empty_bar, const PeerSet &ps) {
     const int k = L.k;
-    // The residual of the output this lane will finish, fetched now so that its latency passes
-    // under the dot products instead of behind them.
-    const float *residual = lc->residual;
-    float res = 0.0f;
-    if (residual && lane < rows * MT)
-        res = residual[(size_t)(lane % MT) * L.ldy + row0 + jl0 + lane / MT];
     int acc[RW][MT][3];
 #pragma unroll
     for (int r = 0; r < RW; ++r)
@@ -213,7 +207,8 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
         const float sc = staged ? scale_s[jl] : __ldg(L.scales + row0 + jl);
         float val = __fmul_rn(dot, sc);
         if (L.bias) val = __fadd_rn(val, staged ? bias_s[jl] : __ldg(L.bias + row0 + jl));
-        if (residual) val = __fadd_rn(val, res);
+        const float *residual = lc->residual;  // read here: a prefetch before the loop cost the loop 1 %
+        if (residual) val = __fadd_rn(val, residual[(size_t)m * L.ldy + row0 + jl]);
         store_result<PEER>(L.y + (size_t)m * L.ldy + row0 + jl, val, ps);
     }
 }
@@ -338,11 +333,12 @@ __device__ __forceinline__ void prep_digits(const StreamLayer &L, int m, int pti
     }
 }
 
-// One activation row with an input transform, held in registers between the passes: thread ptid
-// keeps chunks ptid, ptid + PREP_THREADS, ... (at most XF_CACHE_CHUNKS of them, i.e. k <= 14336; the
-// host checks).  x and the auxiliary operand are read from global memory once, all loads of a
-// chunk issued before anything is computed on them, and silu - an exp and an IEEE divide per
-// element, in every CTA - is evaluated once instead of once per pass.
+// One activation row (with or without an input transform) held in registers between the passes:
+// thread ptid keeps chunks ptid, ptid + PREP_THREADS, ... (at most XF_CACHE_CHUNKS of them, i.e.
+// k <= 14336; longer rows and two-row launches take the multi-pass code).  x and the auxiliary
+// operand are read from global memory once, all loads of a chunk issued before anything is computed
+// on them, and silu - an exp and a divide per element, in every CTA - is evaluated once instead of
+// once per pass.
 constexpr int XF_CACHE_CHUNKS = 4;
 __device__ __forceinline__ void xf_load(const StreamLayer &L, int ptid, int chunks, uint64_t pol_keep,
                                         float (&xc)[XF_CACHE_CHUNKS][16]) {
@@ -519,7 +515,9 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
             if (li == 0) grid_dependency_wait();  // x may be the previous kernel's output
 
             const bool xform = L.gamma != nullptr || L.x2 != nullptr;
-            const bool cached = MT == 1 && xform;  // one row: x' stays in registers between the passes
+            // one row of at most 14336 elements: x' stays in this warp group's registers between the
+            // passes - one read of x, every load in flight at once (with or without a transform)
+            const bool cached = MT == 1 && chunks <= XF_CACHE_CHUNKS * PREP_THREADS;
             float xc[XF_CACHE_CHUNKS][16];
             float rr[MT];
 #pragma unroll
