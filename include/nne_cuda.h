@@ -199,7 +199,7 @@ NNE_API int nne_qlinear_forward_dev_strided(nne_qlinear *ql, const float *x_dev,
 NNE_API int nne_qlinear_forward_dev_static(nne_qlinear *ql, const float *x_dev, size_t m, size_t k,
                                            float *y_dev, void *stream);
 
-/* ---- plan: several independent forwards as one launch --------------------------------------
+/* ---- plan: several forwards as one launch ----------------------------------------------------
  * A plan fixes a list of `count` forwards y_i[m, n_i] = QLinear_i.forward(x_i[m, k_i]) on device
  * buffers that stay in place, and nne_qlinear_plan_run issues all of them on `stream`.  It takes
  * the place of the back-to-back QLinear::forward calls a caller makes on projections that do
@@ -211,7 +211,19 @@ NNE_API int nne_qlinear_forward_dev_static(nne_qlinear *ql, const float *x_dev, 
  * all layers (layers given the same x pointer share one set of digit planes; the work areas are
  * allocated at creation, so a run allocates nothing; a plan must not run concurrently with
  * itself); otherwise the plan runs its layers one after the other.  Results are identical to
- * `count` calls of nne_qlinear_forward_dev.  Layers must outlive the plan.                      */
+ * `count` calls of nne_qlinear_forward_dev.  Layers must outlive the plan.
+ *
+ * Items may also depend on one another: where an item reads a buffer an earlier item of the list
+ * writes (or writes one an earlier item reads or writes), the plan orders them - the list behaves
+ * like `count` forwards issued one after another on a stream.  The dependencies are found from the
+ * pointers when the plan is created.  For m = 1 on streaming shapes the whole list is still ONE
+ * launch: the grid meets between dependent layers (an arrival counter in device memory, bounded
+ * wait, cooperative launch) while the weight stream runs on into the next layer's rows; the
+ * counter carries over from run to run, so such a plan may be captured in a CUDA graph and
+ * replayed, but must not run concurrently with itself.  Other sizes run the independent groups one
+ * after another.  An item whose output overlaps one of its own inputs is refused
+ * (NNE_ERR_INVALID_ARGUMENT), except a residual that is the output buffer itself.  After
+ * NNE_ERR_TIMEOUT a plan with dependent items must be destroyed (its counter is left mid-count). */
 NNE_API int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *layers,
                                     const float *const *x_dev, float *const *y_dev, size_t m,
                                     nne_plan **out);
@@ -253,7 +265,9 @@ NNE_API int nne_add_dev(nne_ctx *ctx, const float *a_dev, const float *b_dev, si
  * leaves the device and launches nothing but the forwards; for other shapes the plan runs the
  * standalone kernels above around its forwards (into buffers it owns).  Results equal the
  * standalone kernels followed by nne_qlinear_forward_dev bit for bit in the second case and within
- * 1e-5 relative in the first (rrms is summed in another order). */
+ * 1e-5 relative in the first (rrms is summed in another order).  Items may consume earlier items'
+ * outputs (see above): a whole decoder block - or a whole stack of them - can be one plan, and at
+ * m = 1 one launch. */
 enum { NNE_INPUT_PLAIN = 0, NNE_INPUT_RMSNORM = 1, NNE_INPUT_SILU_MUL = 2 };
 typedef struct nne_plan_item {
     nne_qlinear *layer;

@@ -710,13 +710,67 @@ int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, siz
 namespace nne {
 namespace {
 
+// Which items of a list have to wait for the items before them: sync[i] = 1 when item i reads
+// something an earlier item (since the last such point) writes, or writes something an earlier one
+// reads or writes.  Byte intervals; a strided output counts from its first to its last element.
+// An item whose own output overlaps its own input is refused (every CTA reads all of x while others
+// already store y), except a residual that IS the output (read and written by the same thread).
+struct ByteRange {
+    uintptr_t lo, hi;
+    bool meets(const ByteRange &o) const { return lo < o.hi && o.lo < hi; }
+};
+ByteRange range_of(const void *p, size_t floats) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    return {a, p ? a + floats * sizeof(float) : a};
+}
+int plan_hazards(size_t count, nne_qlinear *const *layers, const float *const *x, float *const *y, size_t m,
+                 const nne_plan_item *items, std::vector<char> &sync) {
+    sync.assign(count, 0);
+    std::vector<ByteRange> reads, writes;
+    for (size_t i = 0; i < count; ++i) {
+        NNE_TRY(check_layer(layers[i]));
+        const size_t n = layers[i]->n, k = layers[i]->k;
+        if (m == 0 || n == 0) continue;
+        const ByteRange w = range_of(y[i], m * n);
+        ByteRange r[4] = {range_of(x[i], m * k), {0, 0}, {0, 0}, {0, 0}};
+        if (items) {
+            if (items[i].input_op == NNE_INPUT_RMSNORM) r[1] = range_of(items[i].gamma, k);
+            if (items[i].input_op == NNE_INPUT_SILU_MUL) r[1] = range_of(items[i].x2, m * k);
+            if (items[i].residual && items[i].residual != y[i]) r[2] = range_of(items[i].residual, m * n);
+        }
+        for (const ByteRange &q : r)
+            if (q.meets(w))
+                return fail(NNE_ERR_INVALID_ARGUMENT, "item %zu: its output overlaps one of its inputs", i);
+        bool wait = false;
+        for (const ByteRange &q : writes) {
+            wait = wait || q.meets(w);
+            for (const ByteRange &mine : r) wait = wait || q.meets(mine);
+        }
+        for (const ByteRange &q : reads) wait = wait || q.meets(w);
+        if (wait) {
+            sync[i] = 1;
+            reads.clear();
+            writes.clear();
+        }
+        writes.push_back(w);
+        for (const ByteRange &mine : r)
+            if (mine.hi > mine.lo) reads.push_back(mine);
+        if (items && items[i].residual == y[i]) reads.push_back(w);
+    }
+    return NNE_OK;
+}
+
 // Fills the plan's layer lists and decides how it runs (one streaming launch, one small-batch
-// launch, or layer by layer).  y[i] / ldy[i] are where this plan's kernels write.
+// launch, or layer by layer).  y[i] / ldy[i] are where this plan's kernels write.  `sync` (or null)
+// marks the items that wait for the ones before them (plan_hazards): a streaming launch lets its
+// grid meet there; any other list is cut into sub-plans that run one after another.
 int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *layers,
                const float *const *x_dev_in, float *const *y_dev, const size_t *ldy_or_null, size_t m,
-               const nne_plan_item *items = nullptr) {
+               const nne_plan_item *items = nullptr, const char *sync = nullptr) {
     plan->ctx = ctx;
     plan->m = m;
+    bool any_sync = false;
+    for (size_t i = 0; sync && i < count; ++i) any_sync = any_sync || sync[i];
     bool fused = (m >= 1 && m <= 2);
     // Can the whole list run as one streaming launch?  Then that kernel applies the items' input
     // transforms and residuals itself.  Otherwise they become standalone launches around the
@@ -729,6 +783,24 @@ int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *l
                 !(m >= 2 && !skinny_disabled() && ql->tmap_wsk) &&
                 // the decode kernel reads gamma and x2 sixteen bytes at a time
                 (!items || (aligned(items[i].gamma, 16) && aligned(items[i].x2, 16)));
+    }
+    if (any_sync && !fused) {
+        for (size_t i = 0; i < count; ++i) {
+            plan->layers.push_back(layers[i]);
+            plan->x.push_back(x_dev_in[i]);
+            plan->y.push_back(y_dev[i]);
+            plan->ldy.push_back(ldy_or_null ? ldy_or_null[i] : layers[i]->n);
+        }
+        size_t b = 0;
+        for (size_t i = 1; i <= count; ++i) {
+            if (i < count && !sync[i]) continue;
+            nne_plan *sub = new nne_plan();
+            plan->phases.push_back(sub);
+            NNE_TRY(plan_build(sub, ctx, i - b, layers + b, x_dev_in + b, y_dev + b,
+                               ldy_or_null ? ldy_or_null + b : nullptr, m, items ? items + b : nullptr));
+            b = i;
+        }
+        return NNE_OK;
     }
     std::vector<const float *> x_eff(x_dev_in, x_dev_in + count);
     if (items && !fused) {
@@ -797,6 +869,7 @@ int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *l
             L.x2 = items[i].input_op == NNE_INPUT_SILU_MUL ? items[i].x2 : nullptr;
             L.residual = items[i].residual;
         }
+        L.sync = (sync && sync[i]) ? 1 : 0;
         plan->descs.push_back(L);
         fused = fused && aligned(ql->q, 16) && aligned(x_dev[i], 16) && aligned(y_dev[i], 4) &&
                 gemv_tma_supports(ql->n, ql->k, m);
@@ -805,6 +878,18 @@ int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *l
     if (m >= 2 && !skinny_disabled() && skinny_plan_supports(layers, x_dev, y_dev, count, m)) {
         NNE_TRY(skinny_plan_create(ctx, layers, x_dev, y_dev, ldy_or_null, count, m, &plan->skinny));
         plan->fused = false;
+    }
+    if (any_sync && !plan->fused)
+        return fail(NNE_ERR_UNSUPPORTED, "a list with dependent items did not come out as one streaming launch");
+#ifdef NNE_TRACE
+    if (plan->fused) {
+        const size_t gsync_bytes = 16 * 1024;  // + the debug build's time stamps
+#else
+    if (any_sync) {
+        const size_t gsync_bytes = sizeof(unsigned long long);
+#endif
+        NNE_CUDA_TRY(cudaMalloc(&plan->gsync_dev, gsync_bytes));
+        NNE_CUDA_TRY(cudaMemset(plan->gsync_dev, 0, gsync_bytes));
     }
     if (plan->fused && count > (size_t)STREAM_INLINE_LAYERS) {
         NNE_CUDA_TRY(cudaMalloc(&plan->descs_dev, count * sizeof(StreamLayer)));
@@ -817,6 +902,8 @@ int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *l
 void plan_free(nne_plan *plan) {
     if (!plan) return;
     if (plan->ctx) cudaSetDevice(plan->ctx->device);
+    for (nne_plan *sub : plan->phases) plan_free(sub);
+    if (plan->gsync_dev) cudaFree(plan->gsync_dev);
     if (plan->descs_dev) cudaFree(plan->descs_dev);
     if (plan->xform_buf) cudaFree(plan->xform_buf);
     if (plan->segs_dev) cudaFree(plan->segs_dev);
@@ -827,9 +914,13 @@ void plan_free(nne_plan *plan) {
 
 // The plan's forward kernels on `s`, each layer writing y[i] at row stride ldy[i].
 int plan_compute(nne_plan *plan, const PeerSet *peers, cudaStream_t s) {
+    if (!plan->phases.empty()) {
+        for (nne_plan *sub : plan->phases) NNE_TRY(plan_compute(sub, nullptr, s));
+        return NNE_OK;
+    }
     if (plan->fused)
         return launch_stream_batch(plan->ctx, plan->descs.data(), plan->descs_dev, (int)plan->descs.size(),
-                                   plan->m, false, s, peers);
+                                   plan->m, false, s, peers, plan->gsync_dev);
     for (const nne_plan::PreOp &op : plan->pre_ops) {
         if (op.kind == NNE_INPUT_RMSNORM)
             NNE_TRY(launch_rmsnorm(plan->ctx, op.x, op.aux, op.eps, op.rows, op.cols, op.dst, s));
@@ -908,9 +999,12 @@ int nne_qlinear_plan_create(nne_ctx *ctx, size_t count, nne_qlinear *const *laye
     if (count && (!layers || !x_dev || !y_dev))
         return fail(NNE_ERR_INVALID_ARGUMENT, "null layer / x / y array");
     if (count > 0x7fffffffu) return fail(NNE_ERR_INVALID_ARGUMENT, "too many layers");
+    std::vector<char> sync;
+    NNE_TRY(plan_hazards(count, layers, x_dev, y_dev, m, nullptr, sync));
     nne_plan *plan = new nne_plan();
-    int st = plan_build(plan, ctx, count, layers, x_dev, y_dev, nullptr, m);
+    int st = plan_build(plan, ctx, count, layers, x_dev, y_dev, nullptr, m, nullptr, sync.data());
     if (st != NNE_OK) {
+        cudaGetLastError();
         plan_free(plan);
         return st;
     }
@@ -944,8 +1038,10 @@ int nne_qlinear_plan_create_fused(nne_ctx *ctx, size_t count, const nne_plan_ite
         xs[i] = it.x;
         ys[i] = it.y;
     }
+    std::vector<char> sync;
+    NNE_TRY(plan_hazards(count, layers.data(), xs.data(), ys.data(), m, items, sync));
     nne_plan *plan = new nne_plan();
-    int st = plan_build(plan, ctx, count, layers.data(), xs.data(), ys.data(), nullptr, m, items);
+    int st = plan_build(plan, ctx, count, layers.data(), xs.data(), ys.data(), nullptr, m, items, sync.data());
     if (st != NNE_OK) {
         cudaGetLastError();
         plan_free(plan);
@@ -1113,12 +1209,21 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
 
 int nne_qlinear_plan_launches(const nne_plan *plan) {
     if (!plan) return 0;
+    if (!plan->phases.empty()) {
+        int total = 0;
+        for (const nne_plan *sub : plan->phases) total += nne_qlinear_plan_launches(sub);
+        return total;
+    }
     if (plan->fused) return 1;
     const int extra = (int)(plan->pre_ops.size() + plan->post_ops.size());
     const int push = extra + ((plan->group && plan->group->world > 1 && plan->route == 0 && plan->seg_count) ? 1 : 0);  // + slice push kernel
     if (plan->skinny) return 2 + push;  // pre-pass + kernel
     return (int)plan->layers.size() + push;
 }
+
+#ifdef NNE_TRACE
+NNE_API void *nne_debug_plan_trace(nne_plan *plan) { return plan ? plan->gsync_dev : nullptr; }
+#endif
 
 int nne_qlinear_plan_destroy(nne_plan *plan) {
     NNE_GUARD_BEGIN

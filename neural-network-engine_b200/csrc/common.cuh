@@ -163,12 +163,20 @@ struct StreamLayer {
     const float *gamma = nullptr;
     const float *x2 = nullptr;
     const float *residual = nullptr;
+    // 1: the layer reads or overwrites something an earlier layer of the same launch writes (or
+    // overwrites something one reads); the grid meets before its activations are prepared
+    int sync = 0;
 };
 constexpr int STREAM_INLINE_LAYERS = 8;  // descriptors passed in the kernel's parameter block
 struct StreamBatch {
     int count;
     int reuse;  // the same weights appear again later in the list: do not mark them evict-first
     const StreamLayer *dev;  // device copy of the descriptors when count > STREAM_INLINE_LAYERS
+    int pf_bytes;  // how far the weight stream's L2 look-ahead runs in front of the ring (0: off)
+#ifdef NNE_TRACE
+    unsigned long long *trace;  // debug builds: time stamps
+#endif
+    unsigned long long *gsync;  // arrival counter of the launch's rendezvous, or null (no chained layer)
     StreamLayer inl[STREAM_INLINE_LAYERS];
 };
 int stream_rows_per_stage(size_t k);
@@ -180,7 +188,8 @@ int launch_gemv_tma_passes(nne_ctx *ctx, const int8_t *q, const float *scales, c
                            const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                            cudaStream_t s);
 int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
-                        size_t m, bool reuse, cudaStream_t s, const PeerSet *peers = nullptr);
+                        size_t m, bool reuse, cudaStream_t s, const PeerSet *peers = nullptr,
+                        unsigned long long *gsync = nullptr);
 int launch_generic(nne_ctx *ctx, const int8_t *q, const float *scales, const float *bias,
                    const float *x, float *y, size_t n, size_t k, size_t m, size_t ldy,
                    cudaStream_t s);
@@ -231,6 +240,10 @@ struct nne_plan {
     std::vector<size_t> ldy;     // row stride of y[i] in floats
     std::vector<nne::StreamLayer> descs;
     nne::StreamLayer *descs_dev = nullptr;
+    // Items that consume earlier items' outputs: one streaming launch whose grid meets between them
+    // (gsync_dev: its arrival counter), or - other kernels - sub-plans run one after another.
+    unsigned long long *gsync_dev = nullptr;
+    std::vector<nne_plan *> phases;
     nne::SkPlan *skinny = nullptr;  // 2 <= m <= 16: the whole list as one small-batch launch
     // Input transforms and residual adds (nne_qlinear_plan_create_fused) where the forward kernels
     // of this plan do not do them themselves: standalone launches before / after, into plan-owned

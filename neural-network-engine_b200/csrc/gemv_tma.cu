@@ -2,8 +2,9 @@
 //   y[r,j] = (sum_i x[r,i] * q[j,i]) * scales[j] (+ bias[j])   (reference
 //   src/nn/quantized.rs:184-192 with the dot product of :253-324).
 //
-// HBM bound.  One launch serves a LIST of independent layers (a single forward is a list of
-// one): every CTA owns a contiguous range of output rows of each layer, i.e. a contiguous byte
+// HBM bound.  One launch serves a LIST of layers (a single forward is a list of one; a layer
+// marked `sync` consumes what earlier layers of the list wrote, and the grid meets before its
+// activations are prepared): every CTA owns a contiguous range of output rows of each layer, i.e. a contiguous byte
 // range of that layer's [N,K] int8 matrix, and one producer thread streams those ranges, layer
 // after layer, through a shared-memory ring with 1-D bulk copies (cp.async.bulk, 8-24 KB each,
 // several in flight).  The bytes in flight therefore do not depend on registers or on how fast
@@ -11,6 +12,11 @@
 // prepare the next layer's activations the ring keeps filling with that layer's weights.
 // Weights are read from HBM exactly once: algorithmic bytes per layer =
 // N*K + 4N (scales) + 4N*[bias] + 4*m*K + 4*m*N.
+// What bounds the stream is the bytes one SM can have on their way: ring bytes / (time a slot is in
+// flight + time its warp works on it).  Shared memory limits the ring to 100-130 KB, so the producer
+// also asks for the stages 64-192 KB AHEAD of the ring to be brought into L2 (cp.async.bulk.prefetch):
+// the ring's own copy then comes from L2 in well under a microsecond, which is worth 8 % on a
+// 12-layer launch and 20 % on 28672-wide layers.
 //
 // Arithmetic.  Converting int8 weights to f32 costs several instructions per byte, so the
 // contraction runs on the integer dot-product unit instead.  Each activation row is put on a
@@ -81,7 +87,12 @@ struct RingBars {
     uint64_t empty[MAX_SLOTS];   // slot's bytes have been consumed
     uint64_t xs_full[2];         // activation buffer b is prepared (count: prep warps)
     uint64_t xs_empty[2];        // every math warp is done with activation buffer b (count: math warps)
+    uint64_t gsync;              // every math warp has stored its results of the layers before a chained one
     int abort_flag;
+    uint32_t gsync_parity;       // phase of `gsync` the next rendezvous waits for (one thread's variable)
+#ifdef NNE_TRACE
+    int tr_j, tr_jm;
+#endif
     int bad_warp[PREP_WARPS];    // per prep warp: its part of x holds Inf/NaN
     float xmax[PREP_WARPS][2];   // per prep warp and activation row: max |x|
     int bad[2];                  // per buffer: the layer's x holds Inf/NaN
@@ -152,7 +163,11 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
                                               const uint4 *xs, int kpad, int rows, int jl0,
                                               int row0, const LayerConsts *lc, const float *scale_s,
                                               const float *bias_s, bool staged, int lane,
-                                              uint32_t empty_bar, const PeerSet &ps) {
+                                              uint32_t empty_bar, const PeerSet &ps
+#ifdef NNE_TRACE
+                                              , unsigned long long *tr
+#endif
+                                              ) {
     const int k = L.k;
     int acc[RW][MT][3];
 #pragma unroll
@@ -184,6 +199,9 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
                 }
         }
     }
+#ifdef NNE_TRACE
+    if (tr && lane == 0) tr[0] = globaltimer_ns();
+#endif
     // The slot's bytes have been consumed: hand it back to the producer.  Lane 31 arrives, a lane
     // that never stores results: the arrive is a release, and a release issued by a lane whose
     // earlier stores went to a peer GPU would wait for their acknowledgement over NVLink.
@@ -396,6 +414,55 @@ __device__ __forceinline__ void xf_apply_gamma(const StreamLayer &L, int ptid, i
     }
 }
 
+#ifdef NNE_TRACE
+#define NNE_TR_ARG , ((batch.trace && blockIdx.x == 0 && warp == 0 && g / active < 48) ? batch.trace + 800 + (g / active) : nullptr)
+#else
+#define NNE_TR_ARG
+#endif
+#ifdef NNE_TRACE
+// Debug builds only: time stamps of the first rendezvous of CTAs 0, 73 and 147, behind the counter.
+#define NNE_TR(j, e)                                                                                   \
+    do {                                                                                               \
+        const int c_ = blockIdx.x == 0 ? 0 : blockIdx.x == 73 ? 1 : blockIdx.x == 147 ? 2 : -1;        \
+        if (batch.trace && c_ >= 0 && (j) < 16) batch.trace[8 + (c_ * 16 + (j)) * 8 + (e)] = globaltimer_ns(); \
+    } while (0)
+#else
+#define NNE_TR(j, e) do { } while (0)
+#endif
+
+// Grid-wide rendezvous between two layers of one launch, the second of which reads (or overwrites)
+// what the first wrote.  Called by ONE thread per CTA, after every math warp of the CTA has arrived
+// at `gsync` behind its last store.  Arrival is an atomic add with release semantics on a 64-bit
+// counter that only ever grows; the generation is read off the value the add returns (every CTA
+// arrives exactly once per rendezvous, so the counter passes a multiple of the grid size exactly
+// when all have arrived), which keeps a replayed launch - a CUDA graph - correct without any
+// per-launch argument.  The wait is an acquire load, bounded like every other wait.  All CTAs of the
+// grid are resident (cooperative launch, one CTA per SM), so a waiting CTA never keeps the ones it
+// waits for off the GPU.
+__device__ __forceinline__ bool grid_rendezvous(unsigned long long *counter, volatile int *abort_flag,
+                                                int *err) {
+    unsigned long long old;
+    asm volatile("atom.add.release.gpu.global.u64 %0, [%1], 1;" : "=l"(old) : "l"(counter) : "memory");
+    const unsigned long long g = gridDim.x;
+    const unsigned long long target = (old / g + 1ull) * g;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    for (;;) {
+        unsigned long long now;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(now) : "l"(counter) : "memory");
+        if (now >= target) return true;
+        if ((++spins & 0x3f) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                *reinterpret_cast<volatile int *>(err) = 0x100 + 0x18;
+                __threadfence_system();
+                return false;
+            }
+        }
+    }
+}
+
 // MT activation rows per layer (1..2).  `num_slots` ring slots of `slot_bytes`; `kpad_max` = 16-byte
 // chunks per activation row rounded up to 32 for the widest layer; `sb_rows` = capacity of the
 // per-layer scale/bias staging (0: read them from global memory).
@@ -439,7 +506,12 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
             mbar_init(smem_u32(&bars->xs_full[b]), PREP_WARPS);
             mbar_init(smem_u32(&bars->xs_empty[b]), MATH_WARPS);
         }
+        mbar_init(smem_u32(&bars->gsync), MATH_WARPS);
         bars->abort_flag = 0;
+        bars->gsync_parity = 0;
+#ifdef NNE_TRACE
+        bars->tr_j = bars->tr_jm = 0;
+#endif
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -450,24 +522,68 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
         // ---------------- producer: weights only, may run ahead of the previous kernel ----------
         if (lane == 0) {
             const uint64_t pol_stream = batch.reuse ? l2_policy_evict_normal() : l2_policy_evict_first();
+            const uint64_t pol_pf = l2_policy_evict_normal();
             int slot = 0;
             uint32_t phase = 0;
             bool ok = true;
+            // A second cursor runs ahead of the ring through the same sequence of stages and asks
+            // for them to be brought into L2 (batch.pf_bytes beyond what the ring holds).  The
+            // ring's copy of a stage then finds it there, which shortens the time a slot spends in
+            // flight - and the ring, which shared memory limits to about 100-130 KB, is what bounds
+            // the bytes this SM can have on their way.  No extra HBM traffic.
+            // All per-stage state is kept incremental: this loop is one thread's chain of dependent
+            // instructions, and its length per stage (0.3 us) is not far below the time HBM needs
+            // to deliver a stage to one SM.
+            int p_li = -1, p_left = 0, p_rw = 1, p_k = 0;  // look-ahead cursor: layer, rows left in it
+            const int8_t *p_src = nullptr;
+            int ahead = 0;  // bytes asked for and not yet copied into the ring
+#ifdef NNE_TRACE
+            int tr_g = 0;
+#endif
             for (int li = 0; li < batch.count && ok; ++li) {
-                const StreamLayer L = layers[li];
-                int row0, cnt;
-                cta_rows(L.n, (int)blockIdx.x, (int)gridDim.x, row0, cnt);
-                const int nst = (cnt + L.rw - 1) / L.rw;
-                for (int s = 0; s < nst; ++s) {
+                const int8_t *src;
+                int left, rw, k;
+                {
+                    int row0, cnt;
+                    cta_rows(layers[li].n, (int)blockIdx.x, (int)gridDim.x, row0, cnt);
+                    k = layers[li].k;
+                    rw = layers[li].rw;
+                    src = layers[li].q + (size_t)row0 * k;
+                    left = cnt;
+                }
+                const uint32_t stage_bytes = (uint32_t)rw * (uint32_t)k;
+                while (left > 0) {
+                    while (ahead < batch.pf_bytes) {
+                        if (p_left <= 0) {
+                            if (p_li + 1 >= batch.count) break;
+                            ++p_li;
+                            int row0;
+                            cta_rows(layers[p_li].n, (int)blockIdx.x, (int)gridDim.x, row0, p_left);
+                            p_k = layers[p_li].k;
+                            p_rw = layers[p_li].rw;
+                            p_src = layers[p_li].q + (size_t)row0 * p_k;
+                            continue;
+                        }
+                        const int pb = min(p_rw, p_left) * p_k;
+                        bulk_prefetch_l2(p_src, (uint32_t)pb, pol_pf);
+                        p_src += pb;
+                        p_left -= p_rw;
+                        ahead += pb;
+                    }
                     ok = mbar_wait(smem_u32(&bars->empty[slot]), phase ^ 1, abort_flag, err, 0x11);
                     if (!ok) break;
-                    const int rows = min(L.rw, cnt - s * L.rw);
-                    const uint32_t bytes = (uint32_t)rows * (uint32_t)L.k;
+                    const uint32_t bytes = left >= rw ? stage_bytes : (uint32_t)left * (uint32_t)k;
                     const uint32_t full = smem_u32(&bars->full[slot]);
                     mbar_arrive_expect_tx(full, bytes);
-                    bulk_load_1d_hint(smem_u32(ring + (size_t)slot * slot_bytes),
-                                      L.q + (size_t)(row0 + s * L.rw) * L.k, bytes, full, pol_stream);
+                    bulk_load_1d_hint(smem_u32(ring + (size_t)slot * slot_bytes), src, bytes, full, pol_stream);
+                    src += bytes;
+                    left -= rw;
+                    ahead -= (int)bytes;
                     if (++slot == num_slots) { slot = 0; phase ^= 1; }
+#ifdef NNE_TRACE
+                    if (batch.trace && blockIdx.x == 0 && tr_g < 96) batch.trace[512 + tr_g] = globaltimer_ns();
+                    ++tr_g;
+#endif
                 }
             }
             if (!ok) {
@@ -513,6 +629,25 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
                 }
             }
             if (li == 0) grid_dependency_wait();  // x may be the previous kernel's output
+            if (L.sync) {
+                // This layer reads (or overwrites) what earlier layers of the launch wrote: the math
+                // warps of every CTA must have stored those results first.  The weight stream does
+                // not stop meanwhile; the ring fills with this layer's rows.
+                if (L.gamma) {
+                    // gamma is a constant: have it on its way while the grid meets
+                    for (int c = ptid; c < chunks; c += PREP_THREADS)
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(L.gamma + (size_t)c * 16));
+                }
+                if (ptid == 0) {
+                    const uint32_t par = bars->gsync_parity;  // kept in shared memory: registers are short here
+                    bars->gsync_parity = par ^ 1u;
+                    (void)mbar_wait(smem_u32(&bars->gsync), par, abort_flag, err, 0x17);
+                    NNE_TR(bars->tr_j, 0);
+                    (void)grid_rendezvous(batch.gsync, abort_flag, err);
+                    NNE_TR(bars->tr_j, 1);
+                }
+                named_bar_sync(1, PREP_THREADS);
+            }
 
             const bool xform = L.gamma != nullptr || L.x2 != nullptr;
             // one row of at most 14336 elements: x' stays in this warp group's registers between the
@@ -590,6 +725,9 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
                     prep_scan<MT, false>(L, ptid, chunks, pol_keep, rr, mx, bad);
             }
             bad = __any_sync(0xffffffffu, bad);
+#ifdef NNE_TRACE
+            if (L.sync && ptid == 0) NNE_TR(bars->tr_j, 2);
+#endif
             // The buffer (digits, scales, flags) may still be read by math warps working on layer
             // li - num_bufs: wait until all of them have released it.
             (void)mbar_wait(smem_u32(&bars->xs_empty[buf]), (use & 1u) ^ 1u, abort_flag, err, 0x15);
@@ -655,6 +793,12 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
             // publish the buffer to the math warps
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars->xs_full[buf]));
+#ifdef NNE_TRACE
+            if (L.sync && ptid == 0) {
+                NNE_TR(bars->tr_j, 3);
+                bars->tr_j = bars->tr_j + 1;
+            }
+#endif
         }
         return;
     }
@@ -687,39 +831,68 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
                         0x16);
         const int bad = bars->bad[buf];
         const LayerConsts *lc = &bars->lc[buf];
+#ifdef NNE_TRACE
+        if (L.sync && warp == 0 && lane == 0) NNE_TR(bars->tr_jm, 4);
+#endif
 
         // Warp w takes the global stages g with g % num_slots == w.  One slot, one warp: a warp
         // never waits on a barrier that is more than one phase behind it, which is what the
         // parity wait needs to be unambiguous.
         if (warp < num_slots) {
+#ifdef NNE_TRACE
+            const int active = num_slots;
+#endif
+            const int slot = warp;
             int g = g_base + ((warp - g_base % num_slots) + num_slots) % num_slots;
             for (; g < g_base + nst; g += num_slots) {
                 const int s = g - g_base;
                 const uint32_t phase = (uint32_t)(g / num_slots) & 1u;
                 // If the wait runs out the error word is set and every later wait returns at once.
-                (void)mbar_wait(smem_u32(&bars->full[warp]), phase, abort_flag, err, 0x12);
+                (void)mbar_wait(smem_u32(&bars->full[slot]), phase, abort_flag, err, 0x12);
+#ifdef NNE_TRACE
+                if (batch.trace && blockIdx.x == 0 && warp == 0 && lane == 0 && g / active < 48)
+                    batch.trace[640 + (g / active) * 2] = globaltimer_ns();
+#endif
                 const int rows = min(L.rw, cnt - s * L.rw);
-                const uint8_t *st = ring + (size_t)warp * slot_bytes;
-                const uint32_t empty_bar = smem_u32(&bars->empty[warp]);
+                const uint8_t *st = ring + (size_t)slot * slot_bytes;
+                const uint32_t empty_bar = smem_u32(&bars->empty[slot]);
                 if (bad) {
                     consume_stage_fp32<MT, PEER>(L, st, L.rw, rows, s * L.rw, row0, lane, empty_bar, ps,
                                                  &bars->rrms[buf][0]);
                 } else if (L.rw == 4) {
                     consume_stage<MT, 4, PEER>(L, st, xs, kpad, rows, s * 4, row0, lc, scale_s, bias_s,
-                                               staged, lane, empty_bar, ps);
+                                               staged, lane, empty_bar, ps NNE_TR_ARG);
                 } else if (L.rw == 2) {
                     consume_stage<MT, 2, PEER>(L, st, xs, kpad, rows, s * 2, row0, lc, scale_s, bias_s,
-                                               staged, lane, empty_bar, ps);
+                                               staged, lane, empty_bar, ps NNE_TR_ARG);
                 } else {
                     consume_stage<MT, 1, PEER>(L, st, xs, kpad, rows, s, row0, lc, scale_s, bias_s,
-                                               staged, lane, empty_bar, ps);
+                                               staged, lane, empty_bar, ps NNE_TR_ARG);
                 }
+#ifdef NNE_TRACE
+                __syncwarp();
+                if (batch.trace && blockIdx.x == 0 && warp == 0 && lane == 0 && g / active < 48)
+                    batch.trace[640 + (g / active) * 2 + 1] = globaltimer_ns();
+#endif
             }
         }
         g_base += nst;
-        // this warp is done with the layer's activation buffer
+        // this warp is done with the layer's activation buffer - and, where the next layer is chained
+        // to the ones before it, with its stores (the arrive is a release behind the warp barrier)
         __syncwarp();
-        if (lane == 31) mbar_arrive(smem_u32(&bars->xs_empty[buf]));
+#ifdef NNE_TRACE
+        if (warp == 0 && lane == 0) {
+            if (L.sync) {
+                NNE_TR(bars->tr_jm, 5);
+                bars->tr_jm = bars->tr_jm + 1;
+            }
+            if (li + 1 < batch.count && layers[li + 1].sync) NNE_TR(bars->tr_jm, 6);
+        }
+#endif
+        if (lane == 31) {
+            mbar_arrive(smem_u32(&bars->xs_empty[buf]));
+            if (li + 1 < batch.count && layers[li + 1].sync) mbar_arrive(smem_u32(&bars->gsync));
+        }
     }
 }
 
@@ -753,10 +926,17 @@ int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    if (batch.gsync) {
+        // chained layers rendezvous inside the launch: the whole grid has to be resident
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+        cfg.numAttrs = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    }
     cudaError_t e = PEER ? cudaLaunchKernelEx(&cfg, qgemv_stream_peer_kernel<MT>, batch, slots, slot_bytes,
                                               kpad, sb_rows, bufs, ctx->err_word, ps)
                          : cudaLaunchKernelEx(&cfg, qgemv_stream_kernel<MT>, batch, slots, slot_bytes, kpad,
@@ -769,8 +949,18 @@ int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot
 
 }  // namespace
 
-// Rows per stage for a layer: the largest of {4, 2, 1} that keeps a stage within 24 KB.
-int stream_rows_per_stage(size_t k) { return (4 * k <= 24576) ? 4 : (2 * k <= 24576) ? 2 : 1; }
+// Rows per stage for a layer: the largest of {4, 2, 1} that keeps a stage within 24 KB.  (Smaller
+// stages in more slots were measured and lose: issuing a copy costs the producer 0.15-0.3 us whatever
+// its size, and a math warp about 0.6 us per stage beside the 0.05 us per KB.)
+// NNE_STREAM_STAGE_KB overrides the bound.
+int stream_rows_per_stage(size_t k) {
+    static const size_t cap = [] {
+        const char *e = getenv("NNE_STREAM_STAGE_KB");
+        const int kb = e ? atoi(e) : 24;
+        return (size_t)(kb < 1 ? 1 : kb) * 1024;
+    }();
+    return (4 * k <= cap) ? 4 : (2 * k <= cap) ? 2 : 1;
+}
 
 // m = activation rows per layer (1..2); one layer's shape.
 bool gemv_tma_supports(size_t n, size_t k, size_t m) {
@@ -786,7 +976,8 @@ bool gemv_tma_supports(size_t n, size_t k, size_t m) {
 // Launches the streaming kernel over `count` layers (descriptors in host memory `host`; for more
 // than STREAM_INLINE_LAYERS layers `dev` must hold the same descriptors in device memory).
 int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer *dev, int count,
-                        size_t m, bool reuse, cudaStream_t s, const PeerSet *peers) {
+                        size_t m, bool reuse, cudaStream_t s, const PeerSet *peers,
+                        unsigned long long *gsync) {
     if (count <= 0) return NNE_OK;
     if (count > STREAM_INLINE_LAYERS && !dev)
         return fail(NNE_ERR_INVALID_ARGUMENT, "a batch of %d layers needs device descriptors", count);
@@ -794,6 +985,25 @@ int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer
     batch.count = count;
     batch.reuse = reuse ? 1 : 0;
     batch.dev = count > STREAM_INLINE_LAYERS ? dev : nullptr;
+    batch.gsync = nullptr;
+    batch.pf_bytes = 0;
+#ifdef NNE_TRACE
+    batch.trace = gsync;
+#endif
+    for (int i = 0; i < count; ++i)
+        if (host[i].sync) {
+            if (i == 0 || !gsync || (peers && peers->world > 1))
+                return fail(NNE_ERR_INVALID_ARGUMENT, "layer %d: a chained layer needs an earlier one, a counter and no column shards", i);
+            batch.gsync = gsync;
+        }
+    // L2 look-ahead of the weight stream per CTA: 192 KB for a list of layers, 64 KB for a single
+    // layer (measured optima; beyond 256 KB per CTA the look-ahead of 148 CTAs starts to push itself
+    // out of L2).  NNE_STREAM_LOOKAHEAD_KB overrides it, 0 switches it off.
+    static const int lookahead_kb = [] {
+        const char *e = getenv("NNE_STREAM_LOOKAHEAD_KB");
+        return e ? atoi(e) : -1;
+    }();
+    batch.pf_bytes = lookahead_kb >= 0 ? lookahead_kb * 1024 : (count > 1 ? 192 : 64) * 1024;
     size_t kmax = 0, slot_payload = 0, nmax = 0, nmin = (size_t)-1;
     for (int i = 0; i < count; ++i) {
         if (i < STREAM_INLINE_LAYERS) batch.inl[i] = host[i];

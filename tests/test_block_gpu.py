@@ -146,3 +146,110 @@ def test_nonfinite_input_through_a_fused_decode_plan(nne, ctx):
     tol, _ = oracle.tolerance(q, sc, xn)
     assert float((np.abs(out[1] - oracle.forward(q, sc, None, xn)[0]) / tol).max()) <= 2e-2
     plan.close()
+
+
+@pytest.mark.parametrize("m", [1, 2, 8])
+def test_chained_items_in_one_plan(nne, ctx, m):
+    """A whole decoder block's linear layers as ONE plan whose items consume one another's outputs:
+    [q, k, v] <- RMSNorm(h); o <- v, + h -> h2; [gate, up] <- RMSNorm(h2); down <- silu(gate) * up,
+    + h2 -> out.  The library finds the dependencies itself.  m = 1: one launch of the decode kernel
+    whose grid meets between the groups; other m: the groups run one after another.  Must equal, bit
+    for bit, the same groups run as four separate plans, and agree with the oracle's chain."""
+    import torch
+    d, f = 1024, 2816
+    s = torch.cuda.current_stream().cuda_stream
+    eps = 1e-6
+    shapes = {"q": (d, d), "k": (512, d), "v": (d, d), "o": (d, d), "gate": (f, d), "up": (f, d), "down": (d, f)}
+    L = {nm: make(nne, ctx, 600 + i, n, k) for i, (nm, (n, k)) in enumerate(shapes.items())}
+    h = oracle.normal(610, m, (m, d), 0.0, 1.5)
+    g1 = oracle.normal(611, 0, (d,), 1.0, 0.1)
+    g2 = oracle.normal(611, 1, (d,), 1.0, 0.1)
+    hd, g1d, g2d = dev(h), dev(g1), dev(g2)
+
+    def buffers():
+        b = {nm: torch.full((m, n), float("nan"), device="cuda") for nm, (n, _) in shapes.items()}
+        b["h2"] = torch.full((m, d), float("nan"), device="cuda")
+        return b
+
+    def groups(b):
+        return [
+            [{"layer": L[nm][0], "x": hd.data_ptr(), "y": b[nm].data_ptr(), "rmsnorm": (g1d.data_ptr(), eps)}
+             for nm in ("q", "k", "v")],
+            [{"layer": L["o"][0], "x": b["v"].data_ptr(), "y": b["h2"].data_ptr(), "residual": hd.data_ptr()}],
+            [{"layer": L[nm][0], "x": b["h2"].data_ptr(), "y": b[nm].data_ptr(), "rmsnorm": (g2d.data_ptr(), eps)}
+             for nm in ("gate", "up")],
+            [{"layer": L["down"][0], "x": b["gate"].data_ptr(), "y": b["down"].data_ptr(),
+              "silu_mul": b["up"].data_ptr(), "residual": b["h2"].data_ptr()}],
+        ]
+
+    b_sep, b_one = buffers(), buffers()
+    separate = [nne.FusedPlan(g, m, ctx) for g in groups(b_sep)]
+    one = nne.FusedPlan([it for g in groups(b_one) for it in g], m, ctx)
+    for p in separate:
+        p.run(s)
+    for _ in range(3):          # run it again and again: the rendezvous counter carries over
+        one.run(s)
+    torch.cuda.synchronize()
+    ctx.check()
+    if m == 1:
+        assert one.launches == 1
+    else:
+        assert one.launches == sum(p.launches for p in separate)
+    for nm in list(shapes) + ["h2"]:
+        assert torch.equal(b_one[nm].view(torch.int32), b_sep[nm].view(torch.int32)), nm
+    # the oracle's chain on the same codes
+    xn = oracle.rms_norm(h, g1, eps)
+    v = oracle.forward(L["v"][1], L["v"][2], None, xn)
+    h2 = oracle.forward(L["o"][1], L["o"][2], None, v) + h
+    xn2 = oracle.rms_norm(h2, g2, eps)
+    gate = oracle.forward(L["gate"][1], L["gate"][2], None, xn2)
+    up = oracle.forward(L["up"][1], L["up"][2], None, xn2)
+    act = oracle.silu_mul(gate, up)
+    out = oracle.forward(L["down"][1], L["down"][2], None, act) + h2
+    got = b_one["down"].cpu().numpy()
+    rel = float(np.abs(got - out).max() / np.abs(out).max())
+    print(f"chained plan m={m}: launches {one.launches}, max |diff| / max |out| vs the oracle chain {rel:.2e}")
+    assert rel <= 1e-4
+    one.close()
+    for p in separate:
+        p.close()
+
+
+def test_chained_plan_hazards_and_refusals(nne, ctx):
+    """Write-after-write and write-after-read inside one plan are ordered too; an item that would
+    overwrite its own input is refused."""
+    import torch
+    d = 512
+    s = torch.cuda.current_stream().cuda_stream
+    a, qa, sa = make(nne, ctx, 620, d, d)
+    b, qb, sb = make(nne, ctx, 621, d, d)
+    x = oracle.normal(622, 0, (1, d))
+    xd = dev(x)
+    y = torch.zeros(1, d, device="cuda")
+    z = torch.zeros(1, d, device="cuda")
+    # item 0: y = a(x); item 1: z = b(y); item 2: y = b(x)  (overwrites what item 1 reads)
+    plan = nne.FusedPlan([{"layer": a, "x": xd.data_ptr(), "y": y.data_ptr()},
+                          {"layer": b, "x": y.data_ptr(), "y": z.data_ptr()},
+                          {"layer": b, "x": xd.data_ptr(), "y": y.data_ptr()}], 1, ctx)
+    assert plan.launches == 1
+    for _ in range(2):
+        plan.run(s)
+    torch.cuda.synchronize()
+    ctx.check()
+    ya = oracle.forward(qa, sa, None, x)
+    tol, _ = oracle.tolerance(qb, sb, ya)
+    assert float((np.abs(z.cpu().numpy() - oracle.forward(qb, sb, None, ya)) / tol).max()) <= 2e-2
+    tol, _ = oracle.tolerance(qb, sb, x)
+    assert float((np.abs(y.cpu().numpy() - oracle.forward(qb, sb, None, x)) / tol).max()) <= 2e-2
+    plan.close()
+    with pytest.raises(nne.InvalidArgument):
+        nne.FusedPlan([{"layer": a, "x": y.data_ptr(), "y": y.data_ptr()}], 1, ctx)
+    # a residual that IS the output is fine (read and written by the same thread)
+    y.copy_(dev(x))
+    p2 = nne.FusedPlan([{"layer": a, "x": xd.data_ptr(), "y": y.data_ptr(), "residual": y.data_ptr()}], 1, ctx)
+    p2.run(s)
+    torch.cuda.synchronize()
+    ctx.check()
+    tol, _ = oracle.tolerance(qa, sa, x)
+    assert float((np.abs(y.cpu().numpy() - (ya + x)) / tol).max()) <= 2e-2
+    p2.close()

@@ -247,6 +247,34 @@ def test_config4_decoder_stack(nne, ctx):
               f"{b / gms * 1e3:.0f} tokens/s, {total_bytes / gms / 1e6:.0f} GB/s of weights); standalone "
               f"element-wise kernels + one forward per layer {dt_u * 1e3:.2f} ms from Python; "
               f"max |diff| / max |h| = {rel:.2e}")
+        # (c) the whole step - all 224 items - as ONE plan: the library finds which items consume
+        # which outputs.  Batch 1: a single launch of the decode kernel whose grid meets between the
+        # groups while the weight stream runs on; batch 8: the groups one after another.  Same
+        # kernels, same arithmetic: the hidden state must not change by a bit.
+        items = []
+        for li, layer in enumerate(stack):
+            src, dst = hid[li % 2], hid[(li + 1) % 2]
+            L = {nm: type("L", (), {"_live_handle": (lambda self, h=layer[nm]: h), "_ctx": ctx})() for nm, _, _ in NAMES}
+            ga, gf = g_attn[li].data_ptr(), g_ffn[li].data_ptr()
+            items += [{"layer": L[nm], "x": src.data_ptr(), "y": bufs[nm].data_ptr(), "rmsnorm": (ga, eps)}
+                      for nm in ("q", "k", "v")]
+            items.append({"layer": L["o"], "x": bufs["v"].data_ptr(), "y": h2.data_ptr(), "residual": src.data_ptr()})
+            items += [{"layer": L[nm], "x": h2.data_ptr(), "y": bufs[nm].data_ptr(), "rmsnorm": (gf, eps)}
+                      for nm in ("gate", "up")]
+            items.append({"layer": L["down"], "x": bufs["gate"].data_ptr(), "y": dst.data_ptr(),
+                          "silu_mul": bufs["up"].data_ptr(), "residual": h2.data_ptr()})
+        whole = nne.FusedPlan(items, b, ctx)
+        assert whole.launches == (1 if b == 1 else launches)
+        hid[0].copy_(xb)
+        whole.run(stream)
+        torch.cuda.synchronize()
+        ctx.check()
+        assert torch.equal(hid[LAYERS % 2].view(torch.int32), got.view(torch.int32))
+        wms = graph_time_ms(torch, lambda st: [hid[0].copy_(xb), whole.run(st)])
+        print(f"config4 batch {b}, the same decoder blocks as ONE plan of {len(items)} items: "
+              f"{whole.launches} launch(es), {wms:.3f} ms as a CUDA graph ({b / wms * 1e3:.0f} tokens/s, "
+              f"{total_bytes / wms / 1e6:.0f} GB/s of weights)")
+        whole.close()
         for p in fused:
             p.close()
     # The 224 layers as INDEPENDENT forwards, each fed its own N(0,1) activation, all in one plan:
