@@ -870,6 +870,12 @@ int plan_build(nne_plan *plan, nne_ctx *ctx, size_t count, nne_qlinear *const *l
             L.residual = items[i].residual;
         }
         L.sync = (sync && sync[i]) ? 1 : 0;
+        if (i > 0 && !L.sync && ldy_or_null == nullptr) {
+            // (not for column shards: their launches do not take this flag)
+            const StreamLayer &P = plan->descs.back();
+            L.same_input = P.x == L.x && P.k == L.k && P.gamma == L.gamma && P.x2 == L.x2 &&
+                           (L.gamma == nullptr || P.eps == L.eps);
+        }
         plan->descs.push_back(L);
         fused = fused && aligned(ql->q, 16) && aligned(x_dev[i], 16) && aligned(y_dev[i], 4) &&
                 gemv_tma_supports(ql->n, ql->k, m);

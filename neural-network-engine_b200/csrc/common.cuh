@@ -166,12 +166,16 @@ struct StreamLayer {
     // 1: the layer reads or overwrites something an earlier layer of the same launch writes (or
     // overwrites something one reads); the grid meets before its activations are prepared
     int sync = 0;
+    // 1: x, its transform and k are those of the layer before it in the list (and nothing wrote x in
+    // between): the kernel reuses that layer's prepared activations
+    int same_input = 0;
 };
 constexpr int STREAM_INLINE_LAYERS = 8;  // descriptors passed in the kernel's parameter block
 struct StreamBatch {
     int count;
     int reuse;  // the same weights appear again later in the list: do not mark them evict-first
     const StreamLayer *dev;  // device copy of the descriptors when count > STREAM_INLINE_LAYERS
+    int chain;     // some layer has `sync` or `same_input` set: the launch takes the kernel instance with those paths
     int pf_bytes;  // how far the weight stream's L2 look-ahead runs in front of the ring (0: off)
 #ifdef NNE_TRACE
     unsigned long long *trace;  // debug builds: time stamps

@@ -478,7 +478,7 @@ __device__ __forceinline__ bool grid_rendezvous(unsigned long long *counter, vol
 // do.  Nor does it wait for anybody: a waiting CTA would hold its SM, and the completion of the
 // grid, until the slowest rank is through.  The exchange's wait kernel (shard.cu) announces what is
 // still unannounced and waits for the arrivals, on behalf of whoever consumes the gathered result.
-template <int MT, bool PEER>
+template <int MT, bool PEER, bool CHAIN>
 __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_slots, int slot_bytes,
                                             int kpad_max, int sb_rows, int num_bufs, int *err,
                                             const PeerSet &ps) {
@@ -616,6 +616,33 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
             uint4 *xs = xs_all + buf * xs_buf;
             float *scale_s = scale_all + buf * sb_rows, *bias_s = bias_all + buf * sb_rows;
 
+            if (CHAIN && L.same_input && num_bufs == 2 && li > 0) {
+                // The layer multiplies the very activations the layer before it did (q/k/v, gate/up):
+                // copy that layer's digit planes from the other buffer instead of reading, transforming
+                // and digitising x again (0.3 us instead of 2-3: a group of such layers is otherwise
+                // bound by this preparation, not by its weights).
+                (void)mbar_wait(smem_u32(&bars->xs_empty[buf]), (use & 1u) ^ 1u, abort_flag, err, 0x15);
+                named_bar_sync(1, PREP_THREADS);  // every prep thread has written its part of the other buffer
+                const uint4 *from = xs_all + (buf ^ 1) * xs_buf;
+                for (int i = ptid; i < MT * 3 * kpad; i += PREP_THREADS) xs[i] = from[i];
+                if (staged) {
+                    for (int i = ptid; i < cnt; i += PREP_THREADS) {
+                        scale_s[i] = ldg_f1_hint(L.scales + row0 + i, pol_keep);
+                        bias_s[i] = L.bias ? ldg_f1_hint(L.bias + row0 + i, pol_keep) : 0.0f;
+                    }
+                }
+                if (ptid == 0) {
+                    bars->bad[buf] = bars->bad[buf ^ 1];
+                    bars->lc[buf] = bars->lc[buf ^ 1];
+                    bars->lc[buf].residual = L.residual;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) bars->rrms[buf][m] = bars->rrms[buf ^ 1][m];
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->xs_full[buf]));
+                continue;
+            }
+
             // Scales and bias are layer constants: fetch this CTA's rows first.  Unconditional
             // loads from clamped addresses, masked afterwards, so that no predicated register
             // write has to wait for a load that is still in flight.
@@ -629,7 +656,7 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
                 }
             }
             if (li == 0) grid_dependency_wait();  // x may be the previous kernel's output
-            if (L.sync) {
+            if (CHAIN && L.sync) {
                 // This layer reads (or overwrites) what earlier layers of the launch wrote: the math
                 // warps of every CTA must have stored those results first.  The weight stream does
                 // not stop meanwhile; the ring fills with this layer's rows.
@@ -891,7 +918,7 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
 #endif
         if (lane == 31) {
             mbar_arrive(smem_u32(&bars->xs_empty[buf]));
-            if (li + 1 < batch.count && layers[li + 1].sync) mbar_arrive(smem_u32(&bars->gsync));
+            if (CHAIN && li + 1 < batch.count && layers[li + 1].sync) mbar_arrive(smem_u32(&bars->gsync));
         }
     }
 }
@@ -904,20 +931,33 @@ __global__ void __launch_bounds__(THREADS, 1)
 qgemv_stream_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int kpad_max, int sb_rows,
                     int num_bufs, int *err) {
     const PeerSet none;
-    stream_body<MT, false>(batch, num_slots, slot_bytes, kpad_max, sb_rows, num_bufs, err, none);
+    stream_body<MT, false, false>(batch, num_slots, slot_bytes, kpad_max, sb_rows, num_bufs, err, none);
+}
+// The instance for lists whose layers depend on or share the input of their predecessors (`sync`,
+// `same_input`).  Separate, because those paths cost the plain instance three spilled registers and
+// 2 % of its speed when they are compiled into it.
+template <int MT>
+__global__ void __launch_bounds__(THREADS, 1)
+qgemv_stream_chain_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int kpad_max, int sb_rows,
+                          int num_bufs, int *err) {
+    const PeerSet none;
+    stream_body<MT, false, true>(batch, num_slots, slot_bytes, kpad_max, sb_rows, num_bufs, err, none);
 }
 template <int MT>
 __global__ void __maxnreg__(120)
 qgemv_stream_peer_kernel(const StreamBatch batch, int num_slots, int slot_bytes, int kpad_max, int sb_rows,
                          int num_bufs, int *err, const PeerSet ps) {
-    stream_body<MT, true>(batch, num_slots, slot_bytes, kpad_max, sb_rows, num_bufs, err, ps);
+    stream_body<MT, true, false>(batch, num_slots, slot_bytes, kpad_max, sb_rows, num_bufs, err, ps);
 }
 
 template <int MT, bool PEER>
 int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot_bytes, int kpad,
                      int sb_rows, int bufs, size_t smem, int grid, const PeerSet &ps, cudaStream_t s) {
+    const bool chain = batch.chain && !PEER;  // some layer is tied to its predecessors
     if (PEER)
         NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_peer_kernel<MT>, smem));
+    else if (chain)
+        NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_chain_kernel<MT>, smem));
     else
         NNE_TRY(ensure_dynamic_smem(ctx->device, qgemv_stream_kernel<MT>, smem));
     cudaLaunchConfig_t cfg = {};
@@ -939,8 +979,10 @@ int launch_stream_mt(nne_ctx *ctx, const StreamBatch &batch, int slots, int slot
     }
     cudaError_t e = PEER ? cudaLaunchKernelEx(&cfg, qgemv_stream_peer_kernel<MT>, batch, slots, slot_bytes,
                                               kpad, sb_rows, bufs, ctx->err_word, ps)
-                         : cudaLaunchKernelEx(&cfg, qgemv_stream_kernel<MT>, batch, slots, slot_bytes, kpad,
-                                              sb_rows, bufs, ctx->err_word);
+                         : chain ? cudaLaunchKernelEx(&cfg, qgemv_stream_chain_kernel<MT>, batch, slots, slot_bytes,
+                                                      kpad, sb_rows, bufs, ctx->err_word)
+                                 : cudaLaunchKernelEx(&cfg, qgemv_stream_kernel<MT>, batch, slots, slot_bytes, kpad,
+                                                      sb_rows, bufs, ctx->err_word);
     count_launch();
     if (e != cudaSuccess)
         return fail(NNE_ERR_CUDA, "streaming kernel launch failed: %s", cudaGetErrorString(e));
@@ -987,6 +1029,8 @@ int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer
     batch.dev = count > STREAM_INLINE_LAYERS ? dev : nullptr;
     batch.gsync = nullptr;
     batch.pf_bytes = 0;
+    batch.chain = 0;
+    for (int i = 0; i < count; ++i) batch.chain |= (host[i].sync || host[i].same_input) ? 1 : 0;
 #ifdef NNE_TRACE
     batch.trace = gsync;
 #endif
