@@ -102,7 +102,7 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             f = [t.strip() for t in ln.split(",")]
@@ -113,12 +113,16 @@ class ClockSampler:
                 mx.append(float(f[2]))
             except ValueError:
                 continue
+            try:
+                pw.append(float(f[3]))
+            except ValueError:
+                pass
             for nm, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None,
                 "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
-                "reasons": sorted(reasons)}
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons)}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -364,14 +368,34 @@ def run_native(args):
     barrier()
     e0.record(stream)
     h0 = time.perf_counter()
-    for _ in range(args.steps * R):
+    marks = []  # an event after every reported step: shows how the rate develops over the timed region
+    # Flow control on the host: at most 8 x 32 launches are queued ahead of the GPU.  With some 500
+    # launches queued the driver's launch queue fills up, an enqueue then costs the host as long as a
+    # kernel runs (55 us instead of 6), and the next launch no longer reaches the GPU before the
+    # running kernel lets its dependents go: the programmatic overlap between launches is lost and
+    # every launch takes 6-11 us longer (measured per step: 6.62 ms for the first 500 launches, 7.19
+    # up to 1000, 7.7 after).  A host that stays 256 launches ahead never starves the GPU.
+    pace = []
+    for i in range(args.steps * R):
         step()
+        if (i + 1) % 32 == 0:
+            pe = torch.cuda.Event()
+            pe.record(stream)
+            pace.append(pe)
+            if len(pace) > 8:
+                pace.pop(0).synchronize()
+        if (i + 1) % R == 0 and (i + 1) < args.steps * R and len(marks) < 63:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(stream)
+            marks.append(ev)
     host_us_per_launch = (time.perf_counter() - h0) * 1e6 / (args.steps * R)  # enqueue only
     step.drain()  # the last runs' slices have arrived on this rank too
     e1.record(stream)
     barrier()
     launches = lib.nne_launch_count() - launches0
     ms = max_over_ranks(e0.elapsed_time(e1))
+    edges = [e0] + marks + ([e1] if len(marks) == args.steps - 1 else [])
+    step_ms = [round(edges[i].elapsed_time(edges[i + 1]), 4) for i in range(len(edges) - 1)]
     clocks = sampler.stop() if rank == 0 else None
     passes = args.steps * R
     value = step_bytes * world * passes / (ms * 1e-3) / 1e9
@@ -612,6 +636,7 @@ def run_native(args):
                            + ", D2H, sync in every pass)"},
             "gpu_launches": int(launches),
             "host_enqueue_us_per_launch": host_us_per_launch,
+            "step_ms": step_ms,
             "clocks": clocks,
         }
         if e2e_layer is not None:
@@ -735,11 +760,57 @@ def run_stack(nne, lib, ctx, dev, make_layer, peaks, args):
                       "launches": int(lib.nne_qlinear_plan_launches(plan))})
         lib.nne_qlinear_plan_destroy(plan)
         del xs, ys
+    # The same 224 layers as what a decode step really is: a CHAIN of 32 decoder blocks, every
+    # layer fed by the ones before it, with the block's RMSNorm / SiLU*mul / residual steps
+    # (reference src/models/llama.rs:377-392, 343-346) fused into the forwards - ONE plan of 224
+    # dependent items (attention itself is not part of this path: v stands in for its output).
+    chained = []
+    H, F = 4096, 11008
+    gam = [torch.ones(H, device=dev) + 0.05 * torch.randn(H, device=dev) for _ in range(64)]
+    for b in (1, 8):
+        x0 = torch.randn(b, H, device=dev)
+        hid = [torch.empty(b, H, device=dev), torch.empty(b, H, device=dev)]
+        h2 = torch.empty(b, H, device=dev)
+        buf = {nm: torch.empty(b, n, device=dev) for nm, n in (("q", H), ("k", H), ("v", H), ("gate", F), ("up", F))}
+        items = (nne._lib.PlanItem * cnt)()
+        for li in range(32):
+            src, dst = hid[li % 2], hid[(li + 1) % 2]
+            q, k, v, o, gate, up, down = hs[7 * li:7 * li + 7]
+            spec = [(q, src, buf["q"], 1, gam[2 * li], None, None), (k, src, buf["k"], 1, gam[2 * li], None, None),
+                    (v, src, buf["v"], 1, gam[2 * li], None, None), (o, buf["v"], h2, 0, None, None, src),
+                    (gate, h2, buf["gate"], 1, gam[2 * li + 1], None, None), (up, h2, buf["up"], 1, gam[2 * li + 1], None, None),
+                    (down, buf["gate"], dst, 2, None, buf["up"], h2)]
+            for j, (h, x, y, op, g, x2, res) in enumerate(spec):
+                it = items[7 * li + j]
+                it.layer, it.x, it.y, it.input_op, it.eps = getattr(h, "value", h), x.data_ptr(), y.data_ptr(), op, 1e-5
+                it.gamma = g.data_ptr() if g is not None else None
+                it.x2 = x2.data_ptr() if x2 is not None else None
+                it.residual = res.data_ptr() if res is not None else None
+        plan = C.c_void_p()
+        if lib.nne_qlinear_plan_create_fused(ctx.handle, cnt, items, b, C.byref(plan)) != 0:
+            raise RuntimeError(nne._lib.last_error())
+
+        def step():
+            hid[0].copy_(x0)
+            if lib.nne_qlinear_plan_run(plan, stream.cuda_stream) != 0:
+                raise RuntimeError(nne._lib.last_error())
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        iters = 10 if args.steps >= 10 else max(3, args.steps)
+        ms = device_time_ms(torch, stream, step, iters)
+        finite = bool(torch.isfinite(hid[0]).all())
+        nbytes = sum(algorithmic_bytes(n, k, b) for n, k in shapes)
+        chained.append({"batch": b, "ms": ms, "tokens_per_s": b / (ms * 1e-3), "GB/s": nbytes / (ms * 1e-3) / 1e9,
+                        "launches": int(lib.nne_qlinear_plan_launches(plan)), "finite": finite})
+        lib.nne_qlinear_plan_destroy(plan)
     for h in hs:
         lib.nne_qlinear_destroy(h)
-    return {"layers": cnt, "weight_bytes": wbytes, "cases": cases,
-            "note": "224 independent forwards as one plan (batch 1: streaming GEMV; batch 8: small-batch "
-                    "tensor-core kernel)"}
+    return {"layers": cnt, "weight_bytes": wbytes, "cases": cases, "chained": chained,
+            "note": "cases: 224 independent forwards as one plan (batch 1: streaming GEMV; batch 8: small-batch "
+                    "tensor-core kernel).  chained: the same layers as 32 decoder blocks in dependency order "
+                    "with RMSNorm, SiLU*mul and residuals fused, one plan of 224 dependent items issued from "
+                    "the host (batch 1: one launch; batch 8: its groups one after another)"}
 
 
 def run_prefill(nne, lib, ctx, dev, make_layer, peaks, args):

@@ -49,9 +49,9 @@ int fail(int status, const char *fmt, ...) __attribute__((format(printf, 2, 3)))
         return ::nne::fail(NNE_ERR_INVALID_ARGUMENT, "unknown exception");         \
     }
 
-// Longest row the integer tensor-core kernels take: |q| <= 128 times a digit |d| <= 64 is 2^13, and
-// an int32 accumulator in TMEM adds in_features of those, so sums stay exact up to 2^18 terms.
-constexpr size_t NNE_TENSOR_INT_MAX_K = (size_t)1 << 18;
+// Longest row the integer tensor-core kernels take: |q| <= 128 times a digit |d| <= 128 is 2^14, and
+// an int32 accumulator in TMEM adds in_features of those, so sums stay exact below 2^17 terms.
+constexpr size_t NNE_TENSOR_INT_MAX_K = ((size_t)1 << 17) - 1;
 
 // ---- launch counter ----------------------------------------------------------------------
 extern std::atomic<uint64_t> g_launches;
@@ -170,6 +170,26 @@ struct StreamLayer {
     // between): the kernel reuses that layer's prepared activations
     int same_input = 0;
 };
+// The decode kernels (streaming GEMV, small-batch tensor-core kernel) put an activation row on the
+// grid 2^-e with |v| = |rint(x * 2^e)| < 2^ACT_GRID_BITS and split v into ACT_PLANES balanced int8
+// digits of base 2^ACT_DIGIT_BITS.  Two base-256 digits (16 bits): the rounding of x to the grid is
+// then at most 2^-15 of the row's largest |x| per element, i.e. a result error of at most 3 % of the
+// path's tolerance (1e-3 * ||x||inf * scale_j * sum|q_jk|) and typically 0.1 % of it, for two dot
+// products per weight instead of three.  (Three base-128 digits, 2^-21, were the first form.)
+#ifndef NNE_DIGIT_PLANES
+#define NNE_DIGIT_PLANES 2
+#endif
+constexpr int ACT_PLANES = NNE_DIGIT_PLANES;
+constexpr int ACT_DIGIT_BITS = ACT_PLANES == 3 ? 7 : 8;
+constexpr int ACT_GRID_BITS = ACT_PLANES == 3 ? 20 : 15;
+// Exponent e of the grid for a row whose largest |x| is `big` (> 0, finite): big * 2^e lies in
+// [2^(ACT_GRID_BITS-1), 2^ACT_GRID_BITS); with two planes the top digit must stay below 128 after
+// the low one has been split off, hence the margin at the top of the binade.
+__host__ __device__ inline int act_grid_exponent(float big) {
+    int e = ACT_GRID_BITS - 1 - ((big > 0.0f) ? ilogbf(big) : 0);
+    if (ACT_PLANES == 2 && scalbnf(big, e) > 32639.0f) --e;
+    return e;
+}
 constexpr int STREAM_INLINE_LAYERS = 8;  // descriptors passed in the kernel's parameter block
 struct StreamBatch {
     int count;

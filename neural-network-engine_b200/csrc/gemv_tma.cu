@@ -68,6 +68,7 @@ __device__ __forceinline__ float pow2f(int p) {  // 2^p for p in [-126, 127]
     return __int_as_float((127 + p) << 23);
 }
 
+constexpr int NP = ACT_PLANES, DIGIT_BITS = ACT_DIGIT_BITS;
 constexpr int MAX_SLOTS = 8;   // ring slots = math warps
 constexpr int MATH_WARPS = 8;  // warps 0..7: one ring slot each
 constexpr int PREP_WARPS = 7;  // warps 8..14: prepare the next layer's activations
@@ -118,29 +119,30 @@ __host__ __device__ inline void cta_rows(int n, int b, int g, int &row0, int &cn
     cnt = per + (b < rem ? 1 : 0);
 }
 
-// Digits of one 16-element chunk of x on the grid 2^-e: v = rint(x * f1 * f2), |v| <= 2^20,
-// v = d0 + 128 d1 + 16384 d2 with d0, d1 in [-64, 63]; byte b of word w holds element 4w+b.
-__device__ __forceinline__ void chunk_digits(const float (&xv)[16], float f1, float f2, uint4 &o0,
-                                             uint4 &o1, uint4 &o2) {
-    uint32_t d[3][4];
+// Digits of one 16-element chunk of x on the grid 2^-e: v = rint(x * f1 * f2), |v| < 2^ACT_GRID_BITS,
+// v = sum_p d_p * 2^(p * DIGIT_BITS) with balanced digits that fit int8; byte b of word w holds
+// element 4w+b.
+__device__ __forceinline__ void chunk_digits(const float (&xv)[16], float f1, float f2, uint4 (&o)[NP]) {
+    constexpr int HALF = 1 << (DIGIT_BITS - 1), MASK = (1 << DIGIT_BITS) - 1;
+    uint32_t d[NP][4];
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-        d[0][w] = d[1][w] = d[2][w] = 0u;
+#pragma unroll
+        for (int p = 0; p < NP; ++p) d[p][w] = 0u;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const int v = rint_small(xv[4 * w + b] * f1 * f2);  // |v| <= 2^20
-            const int d0 = ((v + 64) & 127) - 64;
-            const int v1 = (v - d0) >> 7;
-            const int d1 = ((v1 + 64) & 127) - 64;
-            const int d2 = (v1 - d1) >> 7;
-            d[0][w] |= (uint32_t)(d0 & 0xff) << (8 * b);
-            d[1][w] |= (uint32_t)(d1 & 0xff) << (8 * b);
-            d[2][w] |= (uint32_t)(d2 & 0xff) << (8 * b);
+            int v = rint_small(xv[4 * w + b] * f1 * f2);
+#pragma unroll
+            for (int p = 0; p < NP - 1; ++p) {
+                const int dp = ((v + HALF) & MASK) - HALF;
+                d[p][w] |= (uint32_t)(dp & 0xff) << (8 * b);
+                v = (v - dp) >> DIGIT_BITS;
+            }
+            d[NP - 1][w] |= (uint32_t)(v & 0xff) << (8 * b);
         }
     }
-    o0 = make_uint4(d[0][0], d[0][1], d[0][2], d[0][3]);
-    o1 = make_uint4(d[1][0], d[1][1], d[1][2], d[1][3]);
-    o2 = make_uint4(d[2][0], d[2][1], d[2][2], d[2][3]);
+#pragma unroll
+    for (int p = 0; p < NP; ++p) o[p] = make_uint4(d[p][0], d[p][1], d[p][2], d[p][3]);
 }
 
 // One stage (RW weight rows in shared memory at `st`) against the digit planes `xs`; the warp's
@@ -169,18 +171,20 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
 #endif
                                               ) {
     const int k = L.k;
-    int acc[RW][MT][3];
+    int acc[RW][MT][NP];
 #pragma unroll
     for (int r = 0; r < RW; ++r)
 #pragma unroll
-        for (int m = 0; m < MT; ++m) acc[r][m][0] = acc[r][m][1] = acc[r][m][2] = 0;
+        for (int m = 0; m < MT; ++m)
+#pragma unroll
+            for (int d = 0; d < NP; ++d) acc[r][m][d] = 0;
 #pragma unroll 2
     for (int c = lane; c < kpad; c += 32) {
-        uint4 xd[MT][3];
+        uint4 xd[MT][NP];
 #pragma unroll
         for (int m = 0; m < MT; ++m)
 #pragma unroll
-            for (int d = 0; d < 3; ++d) xd[m][d] = xs[((size_t)m * 3 + d) * kpad + c];
+            for (int d = 0; d < NP; ++d) xd[m][d] = xs[((size_t)m * NP + d) * kpad + c];
 #pragma unroll
         for (int r = 0; r < RW; ++r) {
             // chunks past the row's end read the next row (or the slot's slack) and meet zero
@@ -189,7 +193,7 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
 #pragma unroll
             for (int m = 0; m < MT; ++m)
 #pragma unroll
-                for (int d = 0; d < 3; ++d) {
+                for (int d = 0; d < NP; ++d) {
                     int a = acc[r][m][d];
                     a = __dp4a((int)wv.x, (int)xd[m][d].x, a);
                     a = __dp4a((int)wv.y, (int)xd[m][d].y, a);
@@ -213,10 +217,11 @@ __device__ __forceinline__ void consume_stage(const StreamLayer &L, const uint8_
     for (int r = 0; r < RW; ++r)
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
-            const int t0 = __reduce_add_sync(0xffffffffu, acc[r][m][0]);
-            const int t1 = __reduce_add_sync(0xffffffffu, acc[r][m][1]);
-            const int t2 = __reduce_add_sync(0xffffffffu, acc[r][m][2]);
-            if (lane == r * MT + m) mine = (double)t0 + 128.0 * (double)t1 + 16384.0 * (double)t2;
+            double tot = 0.0;
+#pragma unroll
+            for (int d = NP - 1; d >= 0; --d)
+                tot = tot * (double)(1 << DIGIT_BITS) + (double)__reduce_add_sync(0xffffffffu, acc[r][m][d]);
+            if (lane == r * MT + m) mine = tot;
         }
     if (lane < rows * MT) {
         const int r = lane / MT, m = lane % MT;
@@ -330,7 +335,9 @@ __device__ __forceinline__ void prep_digits(const StreamLayer &L, int m, int pti
                                             float f1, float f2, float rr, uint4 *plane) {
     const int k = L.k;
     for (int c = ptid; c < kpad; c += PREP_THREADS) {
-        uint4 o0 = make_uint4(0u, 0u, 0u, 0u), o1 = o0, o2 = o0;
+        uint4 o[NP];
+#pragma unroll
+        for (int p = 0; p < NP; ++p) o[p] = make_uint4(0u, 0u, 0u, 0u);
         if (c < chunks) {
             const float4 *p4 = reinterpret_cast<const float4 *>(L.x + (size_t)m * k + (size_t)c * 16);
             float xv[16];
@@ -343,11 +350,10 @@ __device__ __forceinline__ void prep_digits(const StreamLayer &L, int m, int pti
                 xv[4 * v + 2] = t4.z;
                 xv[4 * v + 3] = t4.w;
             }
-            chunk_digits(xv, f1, f2, o0, o1, o2);
+            chunk_digits(xv, f1, f2, o);
         }
-        plane[c] = o0;
-        plane[kpad + c] = o1;
-        plane[2 * kpad + c] = o2;
+#pragma unroll
+        for (int p = 0; p < NP; ++p) plane[p * kpad + c] = o[p];
     }
 }
 
@@ -487,7 +493,7 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
     //         scale_s[num_bufs][sb_rows] | bias_s[num_bufs][sb_rows]
     uint8_t *ring = smem;
     uint4 *xs_all = reinterpret_cast<uint4 *>(smem + (size_t)num_slots * slot_bytes);
-    const size_t xs_buf = (size_t)MT * 3 * kpad_max;
+    const size_t xs_buf = (size_t)MT * NP * kpad_max;
     RingBars *bars = reinterpret_cast<RingBars *>(xs_all + num_bufs * xs_buf);
     float *scale_all = reinterpret_cast<float *>(bars + 1);
     float *bias_all = scale_all + num_bufs * sb_rows;
@@ -624,7 +630,7 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
                 (void)mbar_wait(smem_u32(&bars->xs_empty[buf]), (use & 1u) ^ 1u, abort_flag, err, 0x15);
                 named_bar_sync(1, PREP_THREADS);  // every prep thread has written its part of the other buffer
                 const uint4 *from = xs_all + (buf ^ 1) * xs_buf;
-                for (int i = ptid; i < MT * 3 * kpad; i += PREP_THREADS) xs[i] = from[i];
+                for (int i = ptid; i < MT * NP * kpad; i += PREP_THREADS) xs[i] = from[i];
                 if (staged) {
                     for (int i = ptid; i < cnt; i += PREP_THREADS) {
                         scale_s[i] = ldg_f1_hint(L.scales + row0 + i, pol_keep);
@@ -790,24 +796,23 @@ __device__ __forceinline__ void stream_body(const StreamBatch &batch, int num_sl
                 for (int m = 0; m < MT; ++m) {
                     float big = 0.0f;
                     for (int w = 0; w < PREP_WARPS; ++w) big = fmaxf(big, bars->xmax[w][m]);
-                    const int e = 19 - ((big > 0.0f) ? ilogbf(big) : 0);  // max|x| * 2^e in [2^19, 2^20)
+                    const int e = act_grid_exponent(big);
                     const int e1 = e >> 1, e2 = e - e1;                     // 2^e = 2^e1 * 2^e2, both finite
                     const float f1 = pow2f(e1), f2 = pow2f(e2);
                     if (ptid == 0) {
                         bars->lc[buf].unscale[m][0] = pow2f(-e1);
                         bars->lc[buf].unscale[m][1] = pow2f(-e2);
                     }
-                    uint4 *plane = xs + (size_t)m * 3 * kpad;
+                    uint4 *plane = xs + (size_t)m * NP * kpad;
                     if (cached) {
 #pragma unroll
                         for (int u = 0; u < XF_CACHE_CHUNKS; ++u) {
                             const int c = ptid + u * PREP_THREADS;
                             if (c < kpad) {  // chunks past the row's end hold zeros
-                                uint4 o0, o1, o2;
-                                chunk_digits(xc[u], f1, f2, o0, o1, o2);
-                                plane[c] = o0;
-                                plane[kpad + c] = o1;
-                                plane[2 * kpad + c] = o2;
+                                uint4 o[NP];
+                                chunk_digits(xc[u], f1, f2, o);
+#pragma unroll
+                                for (int p = 0; p < NP; ++p) plane[p * kpad + c] = o[p];
                             }
                         }
                     } else if (xform) {
@@ -1011,7 +1016,7 @@ bool gemv_tma_supports(size_t n, size_t k, size_t m) {
     if (n > 0x7fffffffu) return false;
     // one buffer of digit planes (48 bytes per 16 activations per row) + two slots must fit
     const size_t kpad = ((k >> 4) + 31) & ~(size_t)31;
-    const size_t need = m * 3 * kpad * 16 + 2 * ((size_t)stream_rows_per_stage(k) * k + 640) + 8192;
+    const size_t need = m * NP * kpad * 16 + 2 * ((size_t)stream_rows_per_stage(k) * k + 640) + 8192;
     return need <= 200 * 1024;
 }
 
@@ -1070,7 +1075,7 @@ int launch_stream_batch(nne_ctx *ctx, const StreamLayer *host, const StreamLayer
     if (sb_rows > 4 * PREP_THREADS) sb_rows = 0;  // the prep warps stage at most 4 rows per thread
     // two activation buffers (so the next layer is prepared while this one runs) when the batch has
     // more than one layer and they leave room for at least four ring slots, else one
-    const size_t one_buf = m * 3 * (size_t)kpad * 16 + 2 * (size_t)sb_rows * sizeof(float);
+    const size_t one_buf = m * NP * (size_t)kpad * 16 + 2 * (size_t)sb_rows * sizeof(float);
     const size_t budget = 220 * 1024;
     int bufs = count > 1 ? 2 : 1;
     if (bufs == 2 && 2 * one_buf + sizeof(RingBars) + 256 + 4 * (size_t)slot_bytes > budget) bufs = 1;

@@ -42,15 +42,15 @@ namespace {
 constexpr int SK_BM = 128;    // output channels per tile
 constexpr int SK_BKB = 128;   // bytes (= int8 elements) of K per unit
 constexpr int SK_ROWS = 16;   // activation rows (padded)
-constexpr int SK_N = 48;      // MMA N: 3 digit planes x 16 rows
+constexpr int SK_N = ACT_PLANES * 16;  // MMA N: digit planes x 16 rows
 constexpr int SK_W_BYTES = SK_BM * SK_BKB;  // 16 KB
-constexpr int SK_X_BYTES = SK_N * SK_BKB;   // 6 KB
-constexpr int SK_STAGE_BYTES = SK_W_BYTES + SK_X_BYTES;  // 22 KB, a multiple of 1024
+constexpr int SK_X_BYTES = SK_N * SK_BKB;   // 4 KB
+constexpr int SK_STAGE_BYTES = SK_W_BYTES + SK_X_BYTES;  // 20 KB, a multiple of 1024
 constexpr int SK_STAGES = 8;
 constexpr int SK_BAR_BYTES = 256;
 constexpr int SK_SMEM_BYTES = SK_STAGES * SK_STAGE_BYTES + SK_BAR_BYTES + 1024;
 constexpr int SK_THREADS = 192;
-constexpr uint32_t SK_TMEM_COLS = 128;  // two accumulators of 64 columns (48 used)
+constexpr uint32_t SK_TMEM_COLS = 128;  // two accumulators of 64 columns (SK_N used)
 static_assert(SK_STAGE_BYTES % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 
 __device__ __forceinline__ uint64_t sk_desc(uint32_t smem_addr) {  // K-major, SWIZZLE_128B
@@ -129,7 +129,7 @@ struct alignas(64) SkLayer {
 // One distinct activation matrix of a launch (layers that read the same x share it).
 struct SkInput {
     const float *x;
-    int8_t *xd;      // [48][k]
+    int8_t *xd;      // [SK_N][k]
     float *unscale;  // [16][2]
     int k;
 };
@@ -346,10 +346,9 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
             if (!ok) break;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 64);
-            uint32_t d0[16], d1[16], d2[16];
-            tmem_ld_32x16(taddr, d0);
-            tmem_ld_32x16(taddr + 16, d1);
-            tmem_ld_32x16(taddr + 32, d2);
+            uint32_t dg[ACT_PLANES][16];
+#pragma unroll
+            for (int p = 0; p < ACT_PLANES; ++p) tmem_ld_32x16(taddr + 16 * p, dg[p]);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
@@ -357,8 +356,11 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
 
             long long s[16];
 #pragma unroll
-            for (int r = 0; r < 16; ++r)
-                s[r] = (long long)(int)d0[r] + ((long long)(int)d1[r] << 7) + ((long long)(int)d2[r] << 14);
+            for (int r = 0; r < 16; ++r) {
+                s[r] = 0;
+#pragma unroll
+                for (int p = ACT_PLANES - 1; p >= 0; --p) s[r] = s[r] * (1 << ACT_DIGIT_BITS) + (long long)(int)dg[p][r];
+            }
 
             bool finish = whole;
             if (!whole) {
@@ -439,11 +441,13 @@ skinny_prepass_kernel(const __grid_constant__ SkInput one, const SkInput *__rest
     int8_t *xd = in.xd;
     float *unscale = in.unscale;
     const int n4 = k >> 2;
-    uint32_t *p0 = reinterpret_cast<uint32_t *>(xd + (size_t)row * k);
-    uint32_t *p1 = reinterpret_cast<uint32_t *>(xd + (size_t)(SK_ROWS + row) * k);
-    uint32_t *p2 = reinterpret_cast<uint32_t *>(xd + (size_t)(2 * SK_ROWS + row) * k);
+    uint32_t *pl[ACT_PLANES];
+#pragma unroll
+    for (int p = 0; p < ACT_PLANES; ++p) pl[p] = reinterpret_cast<uint32_t *>(xd + (size_t)(p * SK_ROWS + row) * k);
     if (row >= m) {
-        for (int i = tid; i < n4; i += 256) p0[i] = p1[i] = p2[i] = 0u;
+        for (int i = tid; i < n4; i += 256)
+#pragma unroll
+            for (int p = 0; p < ACT_PLANES; ++p) pl[p][i] = 0u;
         if (tid == 0) unscale[2 * row] = unscale[2 * row + 1] = 0.0f;
         return;
     }
@@ -482,7 +486,7 @@ skinny_prepass_kernel(const __grid_constant__ SkInput one, const SkInput *__rest
         mx = fmaxf(mx, wmax[w]);
         bad |= wbad[w];
     }
-    const int e = 19 - ((mx > 0.0f) ? ilogbf(mx) : 0);
+    const int e = act_grid_exponent(mx);
     const int e1 = e >> 1, e2 = e - e1;  // 2^e = 2^e1 * 2^e2, both factors finite
     const float f1 = __int_as_float((127 + e1) << 23), f2 = __int_as_float((127 + e2) << 23);
     if (tid == 0) {
@@ -492,21 +496,23 @@ skinny_prepass_kernel(const __grid_constant__ SkInput one, const SkInput *__rest
     }
     auto emit = [&](int i, const float4 &t) {
         const float xv[4] = {t.x, t.y, t.z, t.w};
-        uint32_t w0 = 0u, w1 = 0u, w2 = 0u;
+        constexpr int HALF = 1 << (ACT_DIGIT_BITS - 1), MASK = (1 << ACT_DIGIT_BITS) - 1;
+        uint32_t w[ACT_PLANES];
+#pragma unroll
+        for (int p = 0; p < ACT_PLANES; ++p) w[p] = 0u;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-            const int v = bad ? 0 : rint_small(xv[b] * f1 * f2);  // |v| <= 2^20
-            const int d0 = ((v + 64) & 127) - 64;
-            const int v1 = (v - d0) >> 7;
-            const int d1 = ((v1 + 64) & 127) - 64;
-            const int d2 = (v1 - d1) >> 7;
-            w0 |= (uint32_t)(d0 & 0xff) << (8 * b);
-            w1 |= (uint32_t)(d1 & 0xff) << (8 * b);
-            w2 |= (uint32_t)(d2 & 0xff) << (8 * b);
+            int v = bad ? 0 : rint_small(xv[b] * f1 * f2);  // |v| < 2^ACT_GRID_BITS
+#pragma unroll
+            for (int p = 0; p < ACT_PLANES - 1; ++p) {
+                const int dp = ((v + HALF) & MASK) - HALF;
+                w[p] |= (uint32_t)(dp & 0xff) << (8 * b);
+                v = (v - dp) >> ACT_DIGIT_BITS;
+            }
+            w[ACT_PLANES - 1] |= (uint32_t)(v & 0xff) << (8 * b);
         }
-        p0[i] = w0;
-        p1[i] = w1;
-        p2[i] = w2;
+#pragma unroll
+        for (int p = 0; p < ACT_PLANES; ++p) pl[p][i] = w[p];
     };
 #pragma unroll
     for (int u = 0; u < 8; ++u) {

@@ -154,7 +154,8 @@ def test_device_forward_and_strided_output(nne, ctx):
 
 def test_forward_linearity_property_70b_shape(nne, ctx):
     """Config-5-shaped layer slice (K = 8192 and K = 28672): f(a*x) = a*f(x) exactly for a power
-    of two, and f(x1) + f(x2) ~= f(x1 + x2) within fp32 rounding."""
+    of two, and f(x1) + f(x2) ~= f(x1 + x2) within the three forwards' rounding of their activations
+    to the 16-bit grid (5 % of the summed tolerances; the measured ratio is printed)."""
     for n, k in ((512, 8192), (256, 28672)):
         ql, qo, so, b = make_layer(nne, ctx, 76 + k, n, k, bias=False, std=0.015)
         x1 = oracle.normal(77, k, (1, k))
@@ -162,7 +163,10 @@ def test_forward_linearity_property_70b_shape(nne, ctx):
         y1, y2 = ql.forward(x1), ql.forward(x2)
         assert np.array_equal(ql.forward(x1 * np.float32(8.0)), y1 * np.float32(8.0))
         y12 = ql.forward(x1 + x2)
-        assert np.abs(y12 - (y1 + y2)).max() < 1e-4
+        tsum = sum(oracle.tolerance(qo, so, v)[0] for v in (x1, x2, x1 + x2))
+        lin = float((np.abs(y12 - (y1 + y2)) / tsum).max())
+        print(f"70B-shape {k}->{n}: |f(x1+x2) - f(x1) - f(x2)| / summed tolerances = {lin:.3e}")
+        assert lin <= 5e-2
         check_forward(ql, qo, so, None, x1, f"70B-shape {k}->{n} M=1")
 
 
