@@ -20,13 +20,16 @@
 //
 // Arithmetic.  Converting int8 weights to f32 costs several instructions per byte, so the
 // contraction runs on the integer dot-product unit instead.  Each activation row is put on a
-// power-of-two fixed-point grid, v_i = rint(x_i * 2^e) with |v_i| <= 2^20 (e from the row's
-// largest |x|), and v_i is split into three balanced base-128 digits held as int8.  Then
-// sum_i v_i*q_ji = D0 + 128*D1 + 16384*D2 with every D an EXACT int32 dp4a sum, and
+// power-of-two fixed-point grid, v_i = rint(x_i * 2^e) with |v_i| < 2^15 (e from the row's
+// largest |x|), and v_i is split into two balanced base-256 digits held as int8.  Then
+// sum_i v_i*q_ji = D0 + 256*D1 with every D an EXACT int32 dp4a sum, and
 // dot = that * 2^-e, rounded to f32 once.  The only approximation is the rounding of x to the
-// grid: at most 2^-21 * 2^ceil(log2 max|x|) per element, i.e. a result error below 1e-6 of the
-// a-priori bound ||x||inf * scale_j * sum|q_jk| that the path's tolerance is written against
-// (tolerance: 1e-3 of it) - the size of fp32 summation error.  Scale and bias are applied as a
+// grid: at most 2^-15 of the row's largest |x| per element, i.e. a result error of at most 3 % of
+// the path's tolerance (1e-3 * ||x||inf * scale_j * sum|q_jk|) and about 0.1 % of it on random
+// data (the errors of the elements do not add up in one direction).  Three base-128 digits
+// (|v| <= 2^20) were the first form: a third more dot products, digit bytes and shared memory for
+// an error the tolerance does not ask for; measured, the two-digit kernel streams 5-9 % faster.
+// Scale and bias are applied as a
 // separate fp32 multiply and add like the reference (:187-190).  Rows of x that hold Inf or NaN
 // take an fp32 FMA loop in the same kernel, so those propagate as IEEE prescribes.
 //
@@ -328,7 +331,7 @@ __device__ __forceinline__ void prep_scan(const StreamLayer &L, int ptid, int ch
         for (int o = 16; o > 0; o >>= 1) mx[m] = fmaxf(mx[m], __shfl_xor_sync(0xffffffffu, mx[m], o));
     }
 }
-// Pass 2, one row: digits of rint(x' * f1 * f2) into the row's three planes (x is re-read; it is in
+// Pass 2, one row: digits of rint(x' * f1 * f2) into the row's digit planes (x is re-read; it is in
 // L1 now).
 template <bool XF>
 __device__ __forceinline__ void prep_digits(const StreamLayer &L, int m, int ptid, int chunks, int kpad,
@@ -386,7 +389,7 @@ __device__ __forceinline__ void xf_load(const StreamLayer &L, int ptid, int chun
         for (int v = 0; v < 4; ++v) {
             if (L.x2) {
                 // silu with the fast exponential and divide (each within about 2 ulp): every CTA
-                // evaluates the whole row, and the result goes onto a 2^-20 grid right after
+                // evaluates the whole row, and the result goes onto the 16-bit grid right after
                 t[v].x = __fmul_rn(__fdividef(t[v].x, 1.0f + __expf(-t[v].x)), a[v].x);
                 t[v].y = __fmul_rn(__fdividef(t[v].y, 1.0f + __expf(-t[v].y)), a[v].y);
                 t[v].z = __fmul_rn(__fdividef(t[v].z, 1.0f + __expf(-t[v].z)), a[v].z);

@@ -4,14 +4,15 @@
 //
 // The int8 codes are fed to tcgen05.mma.kind::i8 exactly as they lie in memory - no dequantizer,
 // no extra pass over shared memory.  Each activation row is put on a power-of-two fixed-point
-// grid, v = rint(x * 2^e) with |v| <= 2^13 (e from the row's largest |x|), and split into two
-// balanced base-128 digits d0, d1 held as int8 (a small pre-pass).  Two MMAs per k-step accumulate
+// grid, v = rint(x * 2^e) with |v| < 2^15 (e from the row's largest |x|), and split into two
+// balanced base-256 digits d0, d1 held as int8 (a small pre-pass).  Two MMAs per k-step accumulate
 // D0 = X0.W^T and D1 = X1.W^T as EXACT int32 sums in two TMEM accumulators, and the epilogue forms
-// dot = (D0 + 128*D1) * 2^-e, then * scales[j] and + bias[j] as separate fp32 operations like the
+// dot = (D0 + 256*D1) * 2^-e, then * scales[j] and + bias[j] as separate fp32 operations like the
 // reference (:187-190).  The one approximation is the rounding of x to the grid: at most
-// 2^-14 * 2^ceil(log2 max|x_r|) per element, i.e. a result error below 6.2e-5 of the a-priori
+// 2^-15 of the row's largest |x| per element, i.e. a result error below 3.1e-5 of the a-priori
 // bound ||x||inf * scale_j * sum|q_jk| the tolerance is written against (tolerance: 1e-3 of it) -
-// 32 times tighter than rounding x to bf16 could guarantee.  The int8 pipe runs at twice the bf16
+// 128 times tighter than rounding x to bf16 could guarantee, and the same grid as the decode
+// kernels use.  The int8 pipe runs at twice the bf16
 // rate, so two digit MMAs cost what one bf16 MMA would.  A row of x holding Inf or NaN yields NaN
 // for that row.
 //
@@ -77,14 +78,22 @@ __device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64
         : "memory");
 }
 
-// D0 + 128*D1 as one correctly rounded float, without a 64-bit integer or an int->float
+// Exponent of the activation grid: max|x| * 2^e in [2^14, 2^15), one lower where the top digit
+// would not stay below 128 once the balanced low digit has been split off.
+__device__ __forceinline__ int grid_exponent16(float big) {
+    int e = 14 - ((big > 0.0f) ? ilogbf(big) : 0);
+    if (scalbnf(big, e) > 32639.0f) --e;
+    return e;
+}
+
+// D0 + 256*D1 as one correctly rounded float, without a 64-bit integer or an int->float
 // conversion (both are slow-rate instructions): split the sum as top * 2^20 + lo with
 // |top| < 2^19 + 2^11 and 0 <= lo < 2^21, turn each part into a float exactly by adding it to the
 // bit pattern of 1.5 * 2^23, and let one fused multiply-add round once.
 __device__ __forceinline__ float combine(uint32_t d0, uint32_t d1) {
     const int b = (int)d0, a = (int)d1;
-    const int top = (b >> 20) + (a >> 13);
-    const int lo = (b & 0xFFFFF) + ((a & 0x1FFF) << 7);
+    const int top = (b >> 20) + (a >> 12);
+    const int lo = (b & 0xFFFFF) + ((a & 0xFFF) << 8);
     const float ft = __int_as_float(0x4B400000 + top) - 12582912.0f;
     const float fl = __int_as_float(0x4B400000 + lo) - 12582912.0f;
     return fmaf(ft, 1048576.0f, fl);
@@ -354,8 +363,8 @@ qlinear_prefill_i8_kernel(const __grid_constant__ CUtensorMap tmap_w,
 }
 
 // Activation pre-pass: one CTA of 256 threads per row of x [m, k] (k % 16 == 0).  Row max -> e
-// with max|x| * 2^e in [2^12, 2^13); v = rint(x * 2^e); d0 = balanced low digit in [-64, 63],
-// d1 = (v - d0) / 128 in [-64, 64].  unscale[r] = 2^-e (NaN if the row holds Inf/NaN).  The row
+// with max|x| * 2^e in [2^14, 2^15); v = rint(x * 2^e); d0 = balanced low digit in [-128, 127],
+// d1 = (v - d0) / 256 in [-128, 127].  unscale[r] = 2^-e (NaN if the row holds Inf/NaN).  The row
 // is read from memory once: each thread keeps up to 8 float4 of it in registers between the two
 // passes (k <= 8192); longer rows re-read the rest.
 __global__ void __launch_bounds__(256)
@@ -410,7 +419,7 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
             mx = fmaxf(mx, wmax[w]);
             bad |= wbad[w];
         }
-        const int e = 12 - ((mx > 0.0f) ? ilogbf(mx) : 0);
+        const int e = grid_exponent16(mx);
         const int e1 = e >> 1, e2 = e - e1;  // 2^e = 2^e1 * 2^e2, both factors finite
         const float f1 = __int_as_float((127 + e1) << 23), f2 = __int_as_float((127 + e2) << 23);
         if (tid == 0) {
@@ -424,9 +433,9 @@ x_to_digits_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, int8_t 
             uint32_t w0 = 0u, w1 = 0u;
 #pragma unroll
             for (int b = 0; b < 4; ++b) {
-                const int v = bad ? 0 : rint_small(xv[b] * f1 * f2);  // |v| <= 2^13
-                const int d0 = ((v + 64) & 127) - 64;
-                const int d1 = (v - d0) >> 7;
+                const int v = bad ? 0 : rint_small(xv[b] * f1 * f2);  // |v| < 2^15
+                const int d0 = ((v + 128) & 255) - 128;
+                const int d1 = (v - d0) >> 8;
                 w0 |= (uint32_t)(d0 & 0xff) << (8 * b);
                 w1 |= (uint32_t)(d1 & 0xff) << (8 * b);
             }
@@ -507,7 +516,7 @@ x_to_digits_bulk_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, in
             mx = fmaxf(mx, wmax[w]);
             bad |= wbad[w];
         }
-        const int e = 12 - ((mx > 0.0f) ? ilogbf(mx) : 0);
+        const int e = grid_exponent16(mx);
         const int e1 = e >> 1, e2 = e - e1;  // 2^e = 2^e1 * 2^e2, both factors finite
         const float f1 = __int_as_float((127 + e1) << 23), f2 = __int_as_float((127 + e2) << 23);
         if (tid == 0) {
@@ -522,9 +531,9 @@ x_to_digits_bulk_kernel(const float *__restrict__ x, int8_t *__restrict__ x0, in
             uint32_t w0 = 0u, w1 = 0u;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const int v = bad ? 0 : rint_small(xv[c] * f1 * f2);  // |v| <= 2^13
-                const int d0 = ((v + 64) & 127) - 64;
-                const int d1 = (v - d0) >> 7;
+                const int v = bad ? 0 : rint_small(xv[c] * f1 * f2);  // |v| < 2^15
+                const int d0 = ((v + 128) & 255) - 128;
+                const int d1 = (v - d0) >> 8;
                 w0 |= (uint32_t)(d0 & 0xff) << (8 * c);
                 w1 |= (uint32_t)(d1 & 0xff) << (8 * c);
             }
@@ -581,7 +590,7 @@ bool prefill_i8_supports(const nne_qlinear *ql, size_t m) {
 int prefill_i8_prepare_layer(nne_qlinear *ql) {
     ql->tmap_w8 = nullptr;
     if (ql->n == 0 || ql->k == 0 || ql->k % 16 != 0) return NNE_OK;
-    // int32 accumulators in TMEM: exact only up to 2^18 terms of at most 2^13 each
+    // int32 accumulators in TMEM: exact only below 2^17 terms of at most 2^14 each
     if (ql->n > 0x7fffff00u || ql->k > NNE_TENSOR_INT_MAX_K) return NNE_OK;
     if ((reinterpret_cast<uintptr_t>(ql->q) & 15u) != 0) return NNE_OK;
     CUtensorMap *map = new CUtensorMap;

@@ -3,9 +3,9 @@
 //
 // The weights are the M side of the MMA (128 output channels per tile), the activations the N
 // side: the m rows of x go to the same fixed-point grid as in the streaming GEMV
-// (v = rint(x * 2^e), |v| <= 2^20, e from the row's largest |x|; three balanced base-128 int8
-// digits), stacked as 48 "rows" (digit d of activation row r = row 16 d + r).  One
-// tcgen05.mma.kind::i8 of shape 128 x 48 x 32 therefore multiplies 4 KB of weights with all three
+// (v = rint(x * 2^e), |v| < 2^15, e from the row's largest |x|; two balanced base-256 int8
+// digits), stacked as 32 "rows" (digit d of activation row r = row 16 d + r).  One
+// tcgen05.mma.kind::i8 of shape 128 x 32 x 32 therefore multiplies 4 KB of weights with both
 // digit planes of all 16 rows, and the int32 accumulators in TMEM hold EXACT integer sums.  With
 // the same grid and the same final expression, the result for an activation row is bit-identical
 // to what the streaming GEMV gives for that row alone.
@@ -17,7 +17,7 @@
 // the sums into y.
 //
 // Warp roles per CTA (192 threads, 1 CTA per SM):
-//   warp 0      TMA producer: 16 KB weight tile + 6 KB digit tile per unit into an 8-slot ring,
+//   warp 0      TMA producer: 16 KB weight tile + 4 KB digit tile per unit into an 8-slot ring,
 //               SWIZZLE_128B, weights with an L2 evict-first hint
 //   warp 1      one lane issues 4 tcgen05.mma per unit and commits to the slot's mbarrier
 //   warps 2-5   epilogue: tcgen05.ld (TMEM lane = output channel), combine the digits, then either
@@ -115,7 +115,7 @@ __host__ __device__ inline int sk_cta_of(long long total, int g, long long u) {
 // plan keeps an array of them in device memory (written by the host before any launch).
 struct alignas(64) SkLayer {
     CUtensorMap tmap_w;    // q [n][k] int8, boxes of 128 rows x 128 bytes
-    CUtensorMap tmap_x;    // digit planes [48][k] of this layer's activations
+    CUtensorMap tmap_x;    // digit planes [SK_N][k] of this layer's activations
     const float *scales;
     const float *bias;
     float *y;
@@ -414,8 +414,8 @@ qlinear_skinny_i8_kernel(const __grid_constant__ SkLayer one, const SkLayer *__r
 }
 
 // Pre-pass.  Blocks 0 .. 16*count-1: activation row r = block % 16 of input block / 16, x [m, k]
-// (k % 16 == 0) -> three digit planes at rows r, 16 + r, 32 + r of xd [48, k] and the row's 2^-e as
-// two factors (rows >= m: zeros).  Same grid as the streaming GEMV: max|x| * 2^e in [2^19, 2^20).
+// (k % 16 == 0) -> digit plane p at row 16 p + r of xd [SK_N, k] and the row's 2^-e as two factors
+// (rows >= m: zeros).  Same grid as the streaming GEMV (act_grid_exponent).
 // The blocks after those zero the partial-sum workspace and the arrival counters.
 __global__ void __launch_bounds__(256)
 skinny_prepass_kernel(const __grid_constant__ SkInput one, const SkInput *__restrict__ many, int count,

@@ -4,7 +4,7 @@ add, as standalone kernels and fused into the forwards of a plan, against the CP
 restatement of those lines.  Tolerance for the element-wise kernels: 1e-5 relative to the row's
 largest magnitude (the sum of squares is taken in another order than the reference's AVX2 lanes);
 for forwards: the path's tolerance 1e-3 * ||x'||inf * scale_j * sum|q_jk| with x' the transformed
-input, and a tight check at 2e-5 of that bound for the fp-exact decode kernels."""
+input, and a tight check at 2 % of that tolerance for the decode kernels (16-bit activation grid)."""
 import numpy as np
 import pytest
 

@@ -1,7 +1,7 @@
 """GPU parity of the small-batch tensor-core forward (3 <= m <= 16) against the CPU oracle.
 
 The kernel puts each activation row on the same fixed-point grid as the streaming GEMV
-(rint(x * 2^e), max|x| * 2^e in [2^19, 2^20)) and keeps exact integer sums, so besides the
+(rint(x * 2^e), max|x| * 2^e in [2^14, 2^15)) and keeps exact integer sums, so besides the
 tolerance check against the oracle there are two bit-for-bit checks: integer-valued activations
 against the oracle, and every row of a batch against the single-row forward of that row (which
 runs the streaming GEMV, a different kernel)."""
