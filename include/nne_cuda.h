@@ -239,7 +239,11 @@ NNE_API int nne_qlinear_plan_run(nne_plan *plan, void *stream);
  * floats each).  Copies them to and from the plan's device buffers (one copy per run of buffers
  * that continue one another in device memory, so a plan built over one x slab and one y slab
  * costs one copy each way), runs the plan on the context's stream and returns when y_all_host is
- * complete.  Serialised per context like the other *_host entry points.  The reference has no
+ * complete.  When both slabs are pinned host memory (cudaHostAlloc / cudaHostRegister) and the runs
+ * are 16-byte aligned multiples of four floats, the copies are done by two small kernels instead of
+ * the copy engines: they chain with the forward kernels by programmatic dependent launch, so the
+ * weight stream starts while x is still crossing PCIe (about a tenth off the round trip of a
+ * 12-layer decode step).  Serialised per context like the other *_host entry points.  The reference has no
  * counterpart; it is what a caller of QLinear::forward on several independent projections
  * (q/k/v: src/models/llama.rs:226-228) gets instead of one host round trip per projection. */
 NNE_API int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_all_host);

@@ -1108,8 +1108,18 @@ int nne_qlinear_plan_create_sharded(nne_shard_group *group, size_t count, nne_ql
         if (route == 0 && !plan->fused) {
             std::vector<PushSeg> segs;
             plan->stores_itself.assign(count, 0);
+            // A tensor-core forward's epilogue stores every tile world-1 times more.  Up to about
+            // 128 MB leaving the rank per forward that hides under the MMAs (2 ranks, 117 MB: +20 %;
+            // 8 ranks, 59 MB: +60 %); with 205 MB to seven peers the epilogue warps became the
+            // bottleneck (12 times the forward's own time, measured): such layers store locally and
+            // the push kernel copies the slice out afterwards.  NNE_SHARD_EPILOGUE_MAX_MB overrides.
+            static const size_t epilogue_max = [] {
+                const char *e = getenv("NNE_SHARD_EPILOGUE_MAX_MB");
+                return (size_t)(e ? atol(e) : 128) << 20;
+            }();
             for (size_t i = 0; i < count; ++i) {
-                if (!plan->skinny && plan->pre_ops.empty() && plan->post_ops.empty() &&
+                const size_t leaving = m * shards[i]->n * sizeof(float) * (size_t)(group->world - 1);
+                if (!plan->skinny && plan->pre_ops.empty() && plan->post_ops.empty() && leaving <= epilogue_max &&
                     forward_stores_to_peers(shards[i], m, plan->x[i], y_slice[i])) {
                     plan->stores_itself[i] = 1;
                     continue;
@@ -1173,21 +1183,22 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
     const size_t count = plan->layers.size();
     // Neighbouring device buffers that continue one another are moved with one copy; an x
     // several layers share (same pointer, q/k/v) appears once in x_all_host per layer all the same.
+    const bool sharded = plan->group != nullptr;
+    struct Run {
+        float *dev;
+        size_t off, len;  // floats
+    };
+    std::vector<Run> xr, yr;
     size_t i = 0, off = 0;
     while (i < count) {
         size_t j = i, len = 0;
         const float *base = plan->x[i];
         while (j < count && plan->x[j] == base + len) len += plan->m * plan->layers[j++]->k;
-        if (len)
-            NNE_CUDA_TRY(cudaMemcpyAsync(const_cast<float *>(base), x_all_host + off, len * sizeof(float),
-                                         cudaMemcpyHostToDevice, s));
+        if (len) xr.push_back({const_cast<float *>(base), off, len});
         off += len;
         i = j;
     }
-    NNE_TRY(plan_issue(plan, s));
-    if (plan->group && plan->route == 0) NNE_TRY(shard_wait(plan->group, plan->group->epoch.load(), s));
     // What comes back: y_i [m, n_i], or for column shards the gathered y_full_i [m, n_total_i].
-    const bool sharded = plan->group != nullptr;
     i = 0;
     off = 0;
     while (i < count) {
@@ -1197,11 +1208,73 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
             len += plan->m * (sharded ? plan->n_total[j] : plan->layers[j]->n);
             ++j;
         }
-        if (len)
-            NNE_CUDA_TRY(cudaMemcpyAsync(y_all_host + off, base, len * sizeof(float),
-                                         cudaMemcpyDeviceToHost, s));
+        if (len) yr.push_back({base, off, len});
         off += len;
         i = j;
+    }
+    // Pinned host memory has a device alias: a kernel can do the copies.  That is worth it because
+    // kernels chain with programmatic dependent launch where a copy engine's transfer does not:
+    // the forward kernel starts streaming its weights while x is still crossing PCIe, and y leaves
+    // in the tail of the forward kernel's grid.  Taken when both slabs are pinned (first and last
+    // byte checked), the runs are few and everything is 16-byte aligned; NNE_HOST_COPY=engine
+    // switches it off.
+    static const bool engine_only = [] {
+        const char *e = getenv("NNE_HOST_COPY");
+        return e && e[0] == 'e';
+    }();
+    const float *x_alias = nullptr;
+    float *y_alias = nullptr;
+    if (!sharded && !engine_only && xr.size() <= (size_t)HOST_COPY_SEGS && yr.size() <= (size_t)HOST_COPY_SEGS) {
+        if (plan->host_x == x_all_host && plan->host_y == y_all_host) {
+            x_alias = plan->host_x_alias;
+            y_alias = plan->host_y_alias;
+        } else {
+            auto alias_of = [](const void *p, size_t bytes) -> void * {
+                cudaPointerAttributes a0, a1;
+                if (cudaPointerGetAttributes(&a0, p) != cudaSuccess ||
+                    cudaPointerGetAttributes(&a1, static_cast<const char *>(p) + bytes - 1) != cudaSuccess) {
+                    cudaGetLastError();
+                    return nullptr;
+                }
+                if (a0.type != cudaMemoryTypeHost || a1.type != cudaMemoryTypeHost || !a0.devicePointer) return nullptr;
+                return a0.devicePointer;
+            };
+            const size_t xb = (xr.empty() ? 0 : xr.back().off + xr.back().len) * sizeof(float);
+            const size_t yb = (yr.empty() ? 0 : yr.back().off + yr.back().len) * sizeof(float);
+            x_alias = xb ? static_cast<const float *>(alias_of(x_all_host, xb)) : nullptr;
+            y_alias = yb ? static_cast<float *>(alias_of(y_all_host, yb)) : nullptr;
+            plan->host_x = x_all_host;
+            plan->host_y = y_all_host;
+            plan->host_x_alias = x_alias;
+            plan->host_y_alias = y_alias;
+        }
+        bool ok16 = x_alias && y_alias && aligned(x_alias, 16) && aligned(y_alias, 16);
+        for (const Run &r : xr) ok16 = ok16 && aligned(r.dev, 16) && r.off % 4 == 0 && r.len % 4 == 0;
+        for (const Run &r : yr) ok16 = ok16 && aligned(r.dev, 16) && r.off % 4 == 0 && r.len % 4 == 0;
+        if (!ok16) x_alias = nullptr;
+    }
+    if (x_alias) {
+        HostCopySegs in = {}, out = {};
+        for (const Run &r : xr) {
+            in.seg[in.count].src = x_alias + r.off;
+            in.seg[in.count].dst = r.dev;
+            in.seg[in.count++].n4 = r.len / 4;
+        }
+        for (const Run &r : yr) {
+            out.seg[out.count].src = r.dev;
+            out.seg[out.count].dst = y_alias + r.off;
+            out.seg[out.count++].n4 = r.len / 4;
+        }
+        NNE_TRY(launch_host_copy(ctx, in, false, s));
+        NNE_TRY(plan_issue(plan, s));
+        NNE_TRY(launch_host_copy(ctx, out, true, s));
+    } else {
+        for (const Run &r : xr)
+            NNE_CUDA_TRY(cudaMemcpyAsync(r.dev, x_all_host + r.off, r.len * sizeof(float), cudaMemcpyHostToDevice, s));
+        NNE_TRY(plan_issue(plan, s));
+        if (sharded && plan->route == 0) NNE_TRY(shard_wait(plan->group, plan->group->epoch.load(), s));
+        for (const Run &r : yr)
+            NNE_CUDA_TRY(cudaMemcpyAsync(y_all_host + r.off, r.dev, r.len * sizeof(float), cudaMemcpyDeviceToHost, s));
     }
     NNE_CUDA_TRY(cudaStreamSynchronize(s));
     const int word = *ctx->err_host;

@@ -222,6 +222,17 @@ int launch_rmsnorm(nne_ctx *ctx, const float *x, const float *gamma, float eps, 
                    float *y, cudaStream_t s);
 int launch_silu_mul(nne_ctx *ctx, const float *gate, const float *up, size_t n, float *out, cudaStream_t s);
 int launch_add(nne_ctx *ctx, const float *a, const float *b, size_t n, float *out, cudaStream_t s);
+// Copies between pinned host memory and device buffers done by a kernel (elementwise.cu).
+constexpr int HOST_COPY_SEGS = 8;
+struct HostCopySegs {
+    int count;
+    struct {
+        const float *src;
+        float *dst;
+        size_t n4;  // float4 elements
+    } seg[HOST_COPY_SEGS];
+};
+int launch_host_copy(nne_ctx *ctx, const HostCopySegs &segs, bool results_of_previous_kernel, cudaStream_t s);
 
 bool prefill_supports(const nne_qlinear *ql, size_t m);
 int prefill_prepare_layer(nne_qlinear *ql);  // builds the weight TMA descriptor
@@ -268,6 +279,9 @@ struct nne_plan {
     // (gsync_dev: its arrival counter), or - other kernels - sub-plans run one after another.
     unsigned long long *gsync_dev = nullptr;
     std::vector<nne_plan *> phases;
+    // nne_qlinear_plan_run_host: the host slabs seen last and their device aliases (null: not pinned)
+    const float *host_x = nullptr, *host_x_alias = nullptr;
+    float *host_y = nullptr, *host_y_alias = nullptr;
     nne::SkPlan *skinny = nullptr;  // 2 <= m <= 16: the whole list as one small-batch launch
     // Input transforms and residual adds (nne_qlinear_plan_create_fused) where the forward kernels
     // of this plan do not do them themselves: standalone launches before / after, into plan-owned

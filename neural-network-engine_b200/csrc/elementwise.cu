@@ -56,6 +56,23 @@ add_kernel(const float *__restrict__ a, const float *__restrict__ b, size_t n, f
         out[i] = __fadd_rn(a[i], b[i]);
 }
 
+// Up to HOST_COPY_SEGS runs of float4 moved between pinned host memory (through its device alias)
+// and device buffers by the SMs instead of a copy engine.  wait_first: the sources are results of
+// the previous kernel of the stream, which this kernel - launched with programmatic stream
+// serialization - may otherwise overtake.
+__global__ void __launch_bounds__(256)
+host_copy_kernel(const HostCopySegs segs, int wait_first) {
+    if (wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // the kernel after this one may start its prologue (its weight stream) while the copy runs
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    for (int g = 0; g < segs.count; ++g) {
+        const float4 *src = reinterpret_cast<const float4 *>(segs.seg[g].src);
+        float4 *dst = reinterpret_cast<float4 *>(segs.seg[g].dst);
+        const size_t n4 = segs.seg[g].n4;
+        for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n4; i += (size_t)gridDim.x * 256) dst[i] = src[i];
+    }
+}
+
 unsigned grid_for(const nne_ctx *ctx, size_t work_items) {
     size_t blocks = (work_items + 255) / 256;
     const size_t cap = (size_t)ctx->sm_count * 8;
@@ -64,6 +81,27 @@ unsigned grid_for(const nne_ctx *ctx, size_t work_items) {
 }
 
 }  // namespace
+
+int launch_host_copy(nne_ctx *ctx, const HostCopySegs &segs, bool results_of_previous_kernel, cudaStream_t s) {
+    size_t n4 = 0;
+    for (int g = 0; g < segs.count; ++g) n4 = n4 > segs.seg[g].n4 ? n4 : segs.seg[g].n4;
+    if (n4 == 0) return NNE_OK;
+    size_t blocks = (n4 + 255) / 256;
+    if (blocks > 64) blocks = 64;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (results_of_previous_kernel && pdl_enabled()) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, host_copy_kernel, segs, results_of_previous_kernel ? 1 : 0);
+    count_launch();
+    if (e != cudaSuccess) return fail(NNE_ERR_CUDA, "host copy kernel launch failed: %s", cudaGetErrorString(e));
+    return NNE_OK;
+}
 
 int launch_rmsnorm(nne_ctx *ctx, const float *x, const float *gamma, float eps, size_t rows, size_t cols,
                    float *y, cudaStream_t s) {

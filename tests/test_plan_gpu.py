@@ -108,6 +108,44 @@ def test_plan_run_host_equals_single_forwards(nne, ctx, m, slabs):
         plan.run_host(x_all[:-1])
 
 
+@pytest.mark.parametrize("m", [1, 4, 40])
+def test_plan_run_host_from_pinned_memory(nne, ctx, m):
+    """With PINNED host slabs (and 16-byte aligned runs) the host round trip moves x and y with
+    copy kernels chained to the forwards instead of copy-engine transfers: same bits as from
+    pageable memory, run after run, also when the slabs change."""
+    import torch
+    shapes = [(512, 1024, True), (256, 4096, False), (128, 1024, True)]
+    layers, xs, ys, refs = build(nne, ctx, shapes, m, 197 + m)
+    xslab = torch.empty(sum(m * k for _, k, _ in shapes), device="cuda")
+    yslab = torch.full((sum(m * n for n, _, _ in shapes),), float("nan"), device="cuda")
+    xp, yp, xo, yo = [], [], 0, 0
+    for n, k, _ in shapes:
+        xp.append(xslab.data_ptr() + 4 * xo)
+        yp.append(yslab.data_ptr() + 4 * yo)
+        xo += m * k
+        yo += m * n
+    plan = nne.QLinearPlan(layers, xp, yp, m, ctx)
+    x_all = np.concatenate([x.reshape(-1) for (_, x, _) in refs])
+    want = plan.run_host(x_all)                      # pageable memory: copy engines
+    launches0 = nne.load().nne_launch_count()
+    plan.run_host(x_all)
+    per_run = nne.load().nne_launch_count() - launches0
+    xpin = torch.from_numpy(x_all).pin_memory()
+    for trial in range(3):
+        ypin = torch.full((want.size,), float("nan")).pin_memory()
+        launches0 = nne.load().nne_launch_count()
+        got = plan.run_host(xpin.numpy(), ypin.numpy())
+        assert nne.load().nne_launch_count() - launches0 == per_run + 2   # + the two copy kernels
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"trial {trial}"
+    ctx.check()
+    # other activations through the same pinned slab
+    x2 = (x_all * np.float32(0.5)).astype(np.float32)
+    xpin.copy_(torch.from_numpy(x2))
+    got2 = plan.run_host(xpin.numpy(), ypin.numpy())
+    assert np.array_equal(got2.view(np.uint32), plan.run_host(x2).view(np.uint32))
+    ctx.check()
+
+
 @pytest.mark.parametrize("m", [3, 8, 16])
 @pytest.mark.parametrize("shared", [False, True])
 def test_small_batch_plan_equals_single_forwards(nne, ctx, m, shared):
