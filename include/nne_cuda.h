@@ -239,8 +239,9 @@ NNE_API int nne_qlinear_plan_run(nne_plan *plan, void *stream);
  * floats each).  Copies them to and from the plan's device buffers (one copy per run of buffers
  * that continue one another in device memory, so a plan built over one x slab and one y slab
  * costs one copy each way), runs the plan on the context's stream and returns when y_all_host is
- * complete.  When both slabs are pinned host memory (cudaHostAlloc / cudaHostRegister) and the runs
- * are 16-byte aligned multiples of four floats, the copies are done by two small kernels instead of
+ * complete.  When both slabs are pinned host memory (cudaHostAlloc / cudaHostRegister), hold at most
+ * 1 MiB together and the runs are 16-byte aligned multiples of four floats (nne_qlinear_forward_host
+ * does the same for its x and y), the copies are done by two small kernels instead of
  * the copy engines: they chain with the forward kernels by programmatic dependent launch, so the
  * weight stream starts while x is still crossing PCIe (about a tenth off the round trip of a
  * 12-layer decode step).  Serialised per context like the other *_host entry points.  The reference has no

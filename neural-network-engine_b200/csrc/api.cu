@@ -134,6 +134,28 @@ int pick_kernel(const nne_qlinear *ql, size_t m, const float *x, const float *y)
     return 3;
 }
 
+// Copy kernels pay off for latency-bound transfers (decode-sized activations); bulk transfers stay
+// with the copy engines, which move a megabyte in less time than 64 CTAs pull it over PCIe.
+constexpr size_t HOST_COPY_KERNEL_MAX_BYTES = (size_t)1 << 20;
+
+// The device alias of [p, p + bytes) if that is pinned host memory (first and last byte asked), else
+// null.  NNE_HOST_COPY=engine makes it null always.
+void *pinned_alias(const void *p, size_t bytes) {
+    static const bool engine_only = [] {
+        const char *e = getenv("NNE_HOST_COPY");
+        return e && e[0] == 'e';
+    }();
+    if (engine_only || !p || bytes == 0) return nullptr;
+    cudaPointerAttributes a0, a1;
+    if (cudaPointerGetAttributes(&a0, p) != cudaSuccess ||
+        cudaPointerGetAttributes(&a1, static_cast<const char *>(p) + bytes - 1) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    if (a0.type != cudaMemoryTypeHost || a1.type != cudaMemoryTypeHost || !a0.devicePointer) return nullptr;
+    return a0.devicePointer;
+}
+
 // Does a forward of m rows on this layer take a kernel that can store into the peers' windows itself?
 bool forward_stores_to_peers(const nne_qlinear *ql, size_t m, const float *x, const float *y) {
     return ql->k != 0 && pick_kernel(ql, m, x, y) == 2 && !prefill_bf16_forced();
@@ -690,9 +712,32 @@ int nne_qlinear_forward_host(nne_qlinear *ql, const float *x_host, size_t m, siz
     cudaStream_t s = ctx->stream;
     NNE_TRY(ctx->stage_a.reserve(xb ? xb : 4));
     NNE_TRY(ctx->stage_b.reserve(yb));
-    if (xb) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, x_host, xb, cudaMemcpyHostToDevice, s));
-    NNE_TRY(forward_dev(ql, (const float *)ctx->stage_a.ptr, m, k, (float *)ctx->stage_b.ptr, ql->n, s));
-    NNE_CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_b.ptr, yb, cudaMemcpyDeviceToHost, s));
+    // Pinned x and y (16-byte aligned, whole float4s): copy kernels chained to the forward by
+    // programmatic dependent launch instead of copy-engine transfers (see nne_qlinear_plan_run_host).
+    const float *x_alias = nullptr;
+    float *y_alias = nullptr;
+    if (xb && xb + yb <= HOST_COPY_KERNEL_MAX_BYTES && xb % 16 == 0 && yb % 16 == 0 && aligned(x_host, 16) &&
+        aligned(y_host, 16)) {
+        x_alias = static_cast<const float *>(pinned_alias(x_host, xb));
+        y_alias = x_alias ? static_cast<float *>(pinned_alias(y_host, yb)) : nullptr;
+    }
+    if (x_alias && y_alias) {
+        HostCopySegs in = {}, out = {};
+        in.count = out.count = 1;
+        in.seg[0].src = x_alias;
+        in.seg[0].dst = (float *)ctx->stage_a.ptr;
+        in.seg[0].n4 = xb / 16;
+        out.seg[0].src = (const float *)ctx->stage_b.ptr;
+        out.seg[0].dst = y_alias;
+        out.seg[0].n4 = yb / 16;
+        NNE_TRY(launch_host_copy(ctx, in, false, s));
+        NNE_TRY(forward_dev(ql, (const float *)ctx->stage_a.ptr, m, k, (float *)ctx->stage_b.ptr, ql->n, s));
+        NNE_TRY(launch_host_copy(ctx, out, true, s));
+    } else {
+        if (xb) NNE_CUDA_TRY(cudaMemcpyAsync(ctx->stage_a.ptr, x_host, xb, cudaMemcpyHostToDevice, s));
+        NNE_TRY(forward_dev(ql, (const float *)ctx->stage_a.ptr, m, k, (float *)ctx->stage_b.ptr, ql->n, s));
+        NNE_CUDA_TRY(cudaMemcpyAsync(y_host, ctx->stage_b.ptr, yb, cudaMemcpyDeviceToHost, s));
+    }
     NNE_CUDA_TRY(cudaStreamSynchronize(s));
     const int word = *ctx->err_host;
     if (word != 0) {
@@ -1218,35 +1263,15 @@ int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_
     // in the tail of the forward kernel's grid.  Taken when both slabs are pinned (first and last
     // byte checked), the runs are few and everything is 16-byte aligned; NNE_HOST_COPY=engine
     // switches it off.
-    static const bool engine_only = [] {
-        const char *e = getenv("NNE_HOST_COPY");
-        return e && e[0] == 'e';
-    }();
     const float *x_alias = nullptr;
     float *y_alias = nullptr;
-    if (!sharded && !engine_only && xr.size() <= (size_t)HOST_COPY_SEGS && yr.size() <= (size_t)HOST_COPY_SEGS) {
-        if (plan->host_x == x_all_host && plan->host_y == y_all_host) {
-            x_alias = plan->host_x_alias;
-            y_alias = plan->host_y_alias;
-        } else {
-            auto alias_of = [](const void *p, size_t bytes) -> void * {
-                cudaPointerAttributes a0, a1;
-                if (cudaPointerGetAttributes(&a0, p) != cudaSuccess ||
-                    cudaPointerGetAttributes(&a1, static_cast<const char *>(p) + bytes - 1) != cudaSuccess) {
-                    cudaGetLastError();
-                    return nullptr;
-                }
-                if (a0.type != cudaMemoryTypeHost || a1.type != cudaMemoryTypeHost || !a0.devicePointer) return nullptr;
-                return a0.devicePointer;
-            };
-            const size_t xb = (xr.empty() ? 0 : xr.back().off + xr.back().len) * sizeof(float);
-            const size_t yb = (yr.empty() ? 0 : yr.back().off + yr.back().len) * sizeof(float);
-            x_alias = xb ? static_cast<const float *>(alias_of(x_all_host, xb)) : nullptr;
-            y_alias = yb ? static_cast<float *>(alias_of(y_all_host, yb)) : nullptr;
-            plan->host_x = x_all_host;
-            plan->host_y = y_all_host;
-            plan->host_x_alias = x_alias;
-            plan->host_y_alias = y_alias;
+    if (!sharded && xr.size() <= (size_t)HOST_COPY_SEGS && yr.size() <= (size_t)HOST_COPY_SEGS) {
+        // (asked on every call: a cached answer would outlive the allocation it was given for)
+        const size_t xb = (xr.empty() ? 0 : xr.back().off + xr.back().len) * sizeof(float);
+        const size_t yb = (yr.empty() ? 0 : yr.back().off + yr.back().len) * sizeof(float);
+        if (xb + yb <= HOST_COPY_KERNEL_MAX_BYTES) {
+            x_alias = xb ? static_cast<const float *>(pinned_alias(x_all_host, xb)) : nullptr;
+            y_alias = yb ? static_cast<float *>(pinned_alias(y_all_host, yb)) : nullptr;
         }
         bool ok16 = x_alias && y_alias && aligned(x_alias, 16) && aligned(y_alias, 16);
         for (const Run &r : xr) ok16 = ok16 && aligned(r.dev, 16) && r.off % 4 == 0 && r.len % 4 == 0;

@@ -279,9 +279,6 @@ struct nne_plan {
     // (gsync_dev: its arrival counter), or - other kernels - sub-plans run one after another.
     unsigned long long *gsync_dev = nullptr;
     std::vector<nne_plan *> phases;
-    // nne_qlinear_plan_run_host: the host slabs seen last and their device aliases (null: not pinned)
-    const float *host_x = nullptr, *host_x_alias = nullptr;
-    float *host_y = nullptr, *host_y_alias = nullptr;
     nne::SkPlan *skinny = nullptr;  // 2 <= m <= 16: the whole list as one small-batch launch
     // Input transforms and residual adds (nne_qlinear_plan_create_fused) where the forward kernels
     // of this plan do not do them themselves: standalone launches before / after, into plan-owned

@@ -135,7 +135,8 @@ def test_plan_run_host_from_pinned_memory(nne, ctx, m):
         ypin = torch.full((want.size,), float("nan")).pin_memory()
         launches0 = nne.load().nne_launch_count()
         got = plan.run_host(xpin.numpy(), ypin.numpy())
-        assert nne.load().nne_launch_count() - launches0 == per_run + 2   # + the two copy kernels
+        small = 4 * (x_all.size + want.size) <= (1 << 20)   # larger transfers stay with the copy engines
+        assert nne.load().nne_launch_count() - launches0 == per_run + (2 if small else 0)   # the two copy kernels
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"trial {trial}"
     ctx.check()
     # other activations through the same pinned slab
