@@ -622,7 +622,10 @@ def run_native(args):
                          "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "frac_of_nominal_8000": achieved / 8000.0,
-                         "avg_launch_us": per_launch_us, "launches_per_pass": launches_per_step,
+                         "avg_launch_us": per_launch_us,
+                         "median_launch_us": (statistics.median(step_ms) * 1e3 / (R * launches_per_step)) if step_ms else None,
+                         "best_launch_us": (min(step_ms) * 1e3 / (R * launches_per_step)) if step_ms else None,
+                         "launches_per_pass": launches_per_step,
                          "algorithmic_bytes_per_launch": step_bytes / launches_per_step,
                          "traffic": DRAM_TRAFFIC_PER_LAUNCH,
                          "traffic_source": "ncu capture of this kernel on this workload at one GPU (a constant, "

@@ -126,6 +126,27 @@ __host__ __device__ inline void cta_rows(int n, int b, int g, int &row0, int &cn
 // v = sum_p d_p * 2^(p * DIGIT_BITS) with balanced digits that fit int8; byte b of word w holds
 // element 4w+b.
 __device__ __forceinline__ void chunk_digits(const float (&xv)[16], float f1, float f2, uint4 (&o)[NP]) {
+    if constexpr (NP == 2) {
+        // Two base-256 digits straight from the bits of x * 2^e + 1.5 * 2^23: that float's low 23
+        // bits hold v in two's complement, so byte 0 of the word is the balanced low digit (the low
+        // byte of v read as int8) and byte 1 of word + 128 is the high digit, floor((v + 128) / 256).
+        // Four fp/int instructions per element and four byte permutes per four elements.
+        uint32_t lo[4], hi[4];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            uint32_t b[4], c[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                b[i] = __float_as_uint(__fadd_rn(xv[4 * w + i] * f1 * f2, 12582912.0f));
+                c[i] = b[i] + 128u;
+            }
+            lo[w] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+            hi[w] = __byte_perm(__byte_perm(c[0], c[1], 0x0051), __byte_perm(c[2], c[3], 0x0051), 0x5410);
+        }
+        o[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        o[NP - 1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        return;
+    }
     constexpr int HALF = 1 << (DIGIT_BITS - 1), MASK = (1 << DIGIT_BITS) - 1;
     uint32_t d[NP][4];
 #pragma unroll
