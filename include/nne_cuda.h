@@ -244,7 +244,10 @@ NNE_API int nne_qlinear_plan_run(nne_plan *plan, void *stream);
  * does the same for its x and y), the copies are done by two small kernels instead of
  * the copy engines: they chain with the forward kernels by programmatic dependent launch, so the
  * weight stream starts while x is still crossing PCIe (about a tenth off the round trip of a
- * 12-layer decode step).  Serialised per context like the other *_host entry points.  The reference has no
+ * 12-layer decode step).  In a list with dependent items (above) the part of x_all_host that belongs
+ * to an item fed by an earlier item is uploaded like the rest and then overwritten on the device by
+ * that item's result: its contents do not matter.  Serialised per context like the other *_host
+ * entry points.  The reference has no
  * counterpart; it is what a caller of QLinear::forward on several independent projections
  * (q/k/v: src/models/llama.rs:226-228) gets instead of one host round trip per projection. */
 NNE_API int nne_qlinear_plan_run_host(nne_plan *plan, const float *x_all_host, float *y_all_host);
