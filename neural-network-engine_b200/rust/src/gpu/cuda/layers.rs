@@ -78,7 +78,10 @@ impl ToCuda for QLinear {
 
 /// Several forwards on fixed device tensors issued together (`nne_qlinear_plan_*`): q/k/v or
 /// gate/up of a LLaMA block (`src/models/llama.rs:226-228,344-346`) as one launch at batch 1, with
-/// RMSNorm / SiLU-mul / residual taken in the forwards' stride when items ask for them.
+/// RMSNorm / SiLU-mul / residual taken in the forwards' stride when items ask for them.  Items may
+/// read tensors that earlier items of the same plan write (`y` of one as `x`, `silu_mul` or
+/// `residual` of a later one): the library orders them, and at batch 1 a whole decoder block - or
+/// every block between two attention calls - still is one launch.
 pub struct CudaPlan {
     raw: *mut ffi::nne_plan,
     _keep: Vec<CudaTensor>, // inputs and outputs stay alive as long as the plan
