@@ -496,6 +496,19 @@ skinny_prepass_kernel(const __grid_constant__ SkInput one, const SkInput *__rest
     }
     auto emit = [&](int i, const float4 &t) {
         const float xv[4] = {t.x, t.y, t.z, t.w};
+        if constexpr (ACT_PLANES == 2) {
+            // the digits are bytes 0 of word and 1 of word + 128 of x * 2^e + 1.5 * 2^23 (its low 23
+            // bits hold v in two's complement), as in the streaming GEMV
+            uint32_t b[4], c[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                b[j] = __float_as_uint(__fadd_rn(bad ? 0.0f : xv[j] * f1 * f2, 12582912.0f));
+                c[j] = b[j] + 128u;
+            }
+            pl[0][i] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+            pl[ACT_PLANES - 1][i] = __byte_perm(__byte_perm(c[0], c[1], 0x0051), __byte_perm(c[2], c[3], 0x0051), 0x5410);
+            return;
+        }
         constexpr int HALF = 1 << (ACT_DIGIT_BITS - 1), MASK = (1 << ACT_DIGIT_BITS) - 1;
         uint32_t w[ACT_PLANES];
 #pragma unroll
