@@ -770,43 +770,46 @@ def run_stack(nne, lib, ctx, dev, make_layer, peaks, args):
     chained = []
     H, F = 4096, 11008
     gam = [torch.ones(H, device=dev) + 0.05 * torch.randn(H, device=dev) for _ in range(64)]
-    for b in (1, 8):
-        x0 = torch.randn(b, H, device=dev)
-        hid = [torch.empty(b, H, device=dev), torch.empty(b, H, device=dev)]
-        h2 = torch.empty(b, H, device=dev)
-        buf = {nm: torch.empty(b, n, device=dev) for nm, n in (("q", H), ("k", H), ("v", H), ("gate", F), ("up", F))}
-        items = (nne._lib.PlanItem * cnt)()
-        for li in range(32):
-            src, dst = hid[li % 2], hid[(li + 1) % 2]
-            q, k, v, o, gate, up, down = hs[7 * li:7 * li + 7]
-            spec = [(q, src, buf["q"], 1, gam[2 * li], None, None), (k, src, buf["k"], 1, gam[2 * li], None, None),
-                    (v, src, buf["v"], 1, gam[2 * li], None, None), (o, buf["v"], h2, 0, None, None, src),
-                    (gate, h2, buf["gate"], 1, gam[2 * li + 1], None, None), (up, h2, buf["up"], 1, gam[2 * li + 1], None, None),
-                    (down, buf["gate"], dst, 2, None, buf["up"], h2)]
-            for j, (h, x, y, op, g, x2, res) in enumerate(spec):
-                it = items[7 * li + j]
-                it.layer, it.x, it.y, it.input_op, it.eps = getattr(h, "value", h), x.data_ptr(), y.data_ptr(), op, 1e-5
-                it.gamma = g.data_ptr() if g is not None else None
-                it.x2 = x2.data_ptr() if x2 is not None else None
-                it.residual = res.data_ptr() if res is not None else None
-        plan = C.c_void_p()
-        if lib.nne_qlinear_plan_create_fused(ctx.handle, cnt, items, b, C.byref(plan)) != 0:
-            raise RuntimeError(nne._lib.last_error())
-
-        def step():
-            hid[0].copy_(x0)
-            if lib.nne_qlinear_plan_run(plan, stream.cuda_stream) != 0:
+    try:
+        for b in (1, 8):
+            x0 = torch.randn(b, H, device=dev)
+            hid = [torch.empty(b, H, device=dev), torch.empty(b, H, device=dev)]
+            h2 = torch.empty(b, H, device=dev)
+            buf = {nm: torch.empty(b, n, device=dev) for nm, n in (("q", H), ("k", H), ("v", H), ("gate", F), ("up", F))}
+            items = (nne._lib.PlanItem * cnt)()
+            for li in range(32):
+                src, dst = hid[li % 2], hid[(li + 1) % 2]
+                q, k, v, o, gate, up, down = hs[7 * li:7 * li + 7]
+                spec = [(q, src, buf["q"], 1, gam[2 * li], None, None), (k, src, buf["k"], 1, gam[2 * li], None, None),
+                        (v, src, buf["v"], 1, gam[2 * li], None, None), (o, buf["v"], h2, 0, None, None, src),
+                        (gate, h2, buf["gate"], 1, gam[2 * li + 1], None, None), (up, h2, buf["up"], 1, gam[2 * li + 1], None, None),
+                        (down, buf["gate"], dst, 2, None, buf["up"], h2)]
+                for j, (h, x, y, op, g, x2, res) in enumerate(spec):
+                    it = items[7 * li + j]
+                    it.layer, it.x, it.y, it.input_op, it.eps = getattr(h, "value", h), x.data_ptr(), y.data_ptr(), op, 1e-5
+                    it.gamma = g.data_ptr() if g is not None else None
+                    it.x2 = x2.data_ptr() if x2 is not None else None
+                    it.residual = res.data_ptr() if res is not None else None
+            plan = C.c_void_p()
+            if lib.nne_qlinear_plan_create_fused(ctx.handle, cnt, items, b, C.byref(plan)) != 0:
                 raise RuntimeError(nne._lib.last_error())
-        for _ in range(3):
-            step()
-        torch.cuda.synchronize()
-        iters = 10 if args.steps >= 10 else max(3, args.steps)
-        ms = device_time_ms(torch, stream, step, iters)
-        finite = bool(torch.isfinite(hid[0]).all())
-        nbytes = sum(algorithmic_bytes(n, k, b) for n, k in shapes)
-        chained.append({"batch": b, "ms": ms, "tokens_per_s": b / (ms * 1e-3), "GB/s": nbytes / (ms * 1e-3) / 1e9,
-                        "launches": int(lib.nne_qlinear_plan_launches(plan)), "finite": finite})
-        lib.nne_qlinear_plan_destroy(plan)
+
+            def step():
+                hid[0].copy_(x0)
+                if lib.nne_qlinear_plan_run(plan, stream.cuda_stream) != 0:
+                    raise RuntimeError(nne._lib.last_error())
+            for _ in range(3):
+                step()
+            torch.cuda.synchronize()
+            iters = 10 if args.steps >= 10 else max(3, args.steps)
+            ms = device_time_ms(torch, stream, step, iters)
+            finite = bool(torch.isfinite(hid[0]).all())
+            nbytes = sum(algorithmic_bytes(n, k, b) for n, k in shapes)
+            chained.append({"batch": b, "ms": ms, "tokens_per_s": b / (ms * 1e-3), "GB/s": nbytes / (ms * 1e-3) / 1e9,
+                            "launches": int(lib.nne_qlinear_plan_launches(plan)), "finite": finite})
+            lib.nne_qlinear_plan_destroy(plan)
+    except RuntimeError as e:  # reported, not fatal: the headline figures above stand on their own
+        chained.append({"unavailable": str(e)[:200]})
     for h in hs:
         lib.nne_qlinear_destroy(h)
     return {"layers": cnt, "weight_bytes": wbytes, "cases": cases, "chained": chained,

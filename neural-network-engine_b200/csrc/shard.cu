@@ -191,8 +191,12 @@ int shard_push(nne_shard_group *g, const PushSeg *segs_dev, int count, size_t fl
     const PeerSet ps = shard_peerset(g, epoch);
     size_t blocks = (floats_total / 4 + 255) / 256;
     if (blocks < 1) blocks = 1;
-    // A copy to G - 1 peers is bound by NVLink, not by SMs: a quarter of the GPU keeps the links busy.
-    const size_t cap = (size_t)(g->ctx->sm_count > 4 ? g->ctx->sm_count / 4 : 1) * 4;
+    // A copy to G - 1 peers is bound by NVLink, not by SMs: for the small slices of decode-sized
+    // forwards one CTA per SM keeps the links busy.  A large slice (tens of MB: a prefill output) needs
+    // more stores in flight than that - 148 CTAs moved 205 MB to seven peers at 320 GB/s - so it gets
+    // four CTAs per SM.
+    size_t cap = (size_t)(g->ctx->sm_count > 4 ? g->ctx->sm_count / 4 : 1) * 4;
+    if (floats_total * sizeof(float) >= ((size_t)16 << 20)) cap *= 4;
     if (blocks > cap) blocks = cap;
     cudaLaunchAttribute pdl[1];
     pdl[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
