@@ -634,9 +634,10 @@ def run_native(args):
                              "sample": cpu_sample},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps,
-                    "api": "nne_qlinear_plan_run_host (pinned host x and y slabs; H2D, one launch"
+                    "api": "nne_qlinear_plan_run_host (pinned host x and y slabs; x host->device, one launch"
                            + (", exchange of the output slices" if world > 1 else "")
-                           + ", D2H, sync in every pass)"},
+                           + ", y device->host, sync in every pass; at one GPU the two copies are made by "
+                             "copy kernels reading and writing the pinned memory over PCIe, chained to the forward)"},
             "gpu_launches": int(launches),
             "host_enqueue_us_per_launch": host_us_per_launch,
             "step_ms": step_ms,
